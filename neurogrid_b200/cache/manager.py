@@ -1,7 +1,8 @@
 """The cache manager: which pages and which slot each live request holds.
 
 Layers declare what they need to keep between steps (:class:`PagedNeed`: keys and values
-that grow with the tokens, all of them or a window; :class:`SlotNeed`: state of fixed size).
+that grow with the tokens, all of them or a window; :class:`SlotNeed`: state of fixed size;
+or a tuple of these, for a layer that keeps several things).
 Layers with the same need form a *group*; each paged group has pages and block tables of
 its own, each slot group one tensor indexed by the request's slot.  Pages are taken as
 tokens are scheduled (never ahead for a whole request), are given back when the request ends
@@ -25,10 +26,13 @@ from .pages import OutOfPages, OutOfSlots, PagePool, SlotPool
 
 @dataclass(frozen=True)
 class PagedNeed:
-    """Keys and values per token: ``n_kv_heads * head_dim`` each; ``window`` None = keep all."""
+    """Keys and values per token: ``n_kv_heads * head_dim`` each; ``window`` None = keep all.
+    ``values`` False: one vector per token and head only (a layer that caches a latent from which
+    it forms keys and values itself); such pages have no value half."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)

@@ -2,7 +2,7 @@
 
 Layers with the same need share a group.  A paged group holds, for each of its layers,
 keys and values as ``[pages, n_kv_heads, page_size, head_dim]`` in the compute dtype; one
-page id is valid in every layer of its group.  A slot group holds ``[layers, slots, *shape]``
+page id is valid in every layer of its group.  Pages of a need without values have no value half.  A slot group holds ``[layers, slots, *shape]``
 in the element type its need names, set to the need's initial value when a request starts.  The reference keeps one pool per attention layer in fp16
 (gpu/cuda/paged_attention.cu:34-67) and conv states on the host between steps.
 """
@@ -37,26 +37,29 @@ class CacheStorage:
         self.layers: Dict[int, LayerCache] = {}
         counts_p: List[int] = []
         counts_s: List[int] = []
-        for cid in sorted(needs):
-            need = needs[cid]
+        def place(need) -> LayerCache:
             if need is None:
-                self.layers[cid] = LayerCache("none")
-            elif isinstance(need, PagedNeed):
+                return LayerCache("none")
+            if isinstance(need, PagedNeed):
                 if need not in self.paged_needs:
                     self.paged_needs.append(need)
                     counts_p.append(0)
                 g = self.paged_needs.index(need)
-                self.layers[cid] = LayerCache("paged", g, counts_p[g])
                 counts_p[g] += 1
-            elif isinstance(need, SlotNeed):
+                return LayerCache("paged", g, counts_p[g] - 1)
+            if isinstance(need, SlotNeed):
                 if need not in self.slot_needs:
                     self.slot_needs.append(need)
                     counts_s.append(0)
                 g = self.slot_needs.index(need)
-                self.layers[cid] = LayerCache("slot", g, counts_s[g])
                 counts_s[g] += 1
-            else:
-                raise TypeError(f"a layer declared an unknown cache need: {need!r}")
+                return LayerCache("slot", g, counts_s[g] - 1)
+            raise TypeError(f"a layer declared an unknown cache need: {need!r}")
+
+        # a layer that keeps several things declares a tuple of needs and is handed a tuple of views
+        for cid in sorted(needs):
+            need = needs[cid]
+            self.layers[cid] = tuple(place(n) for n in need) if isinstance(need, tuple) else place(need)
         self.pages_per_group = [pages_per_group(n) if callable(pages_per_group) else int(pages_per_group)
                                 for n in self.paged_needs]
         self.k: List[torch.Tensor] = []
@@ -64,7 +67,7 @@ class CacheStorage:
         for need, n_layers, pages in zip(self.paged_needs, counts_p, self.pages_per_group):
             shape = (n_layers, pages, need.n_kv_heads, page_size, need.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape, dtype=dtype, device=device) if need.values else None)
         for need in self.slot_needs:
             if need.dtype not in _SLOT_DTYPES:
                 raise TypeError(f"a layer asks for state of dtype {need.dtype!r}; one of {sorted(_SLOT_DTYPES)}")
@@ -80,7 +83,8 @@ class CacheStorage:
 
     def bytes_per_token(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * k.shape[0] * n.n_kv_heads * n.head_dim * esz for k, n in zip(self.k, self.paged_needs))
+        return sum((2 if n.values else 1) * k.shape[0] * n.n_kv_heads * n.head_dim * esz
+                   for k, n in zip(self.k, self.paged_needs))
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v + self.state)
+        return sum(t.numel() * t.element_size() for t in self.k + self.v + self.state if t is not None)

@@ -1,5 +1,7 @@
 from .lfm2 import ConfigError, Lfm2Config
+from .metanex import MetanexConfig
 from .registry import (architecture_name, config_from_dict, load_config, register_architecture,
                        registered_architectures)
-from .specs import (AttentionSpec, LayerSpec, ModelSpec, NoPositionSpec, RMSNormSpec, RopeSpec,
-                    ScheduleEntry, ShortConvSpec, SwiGLUSpec)
+from .specs import (AttentionSpec, InputConvSpec, LatentAttentionSpec, LayerSpec, ModelSpec, MoESpec, NoPositionSpec,
+                    RMSNormSpec, RetentionSpec, RopeSpec, ScalarRMSNormSpec, ScheduleEntry, ShortConvSpec, SwiGLUSpec,
+                    TokenSideSpec)

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to its
+"""One registry from an architecture's name (config.json ``architectures[0]`` or ``architecture``) to its
 typed configuration class.  A configuration class offers ``from_dict(mapping)`` and
 ``model_spec()``; that is all the rest of the framework asks of an architecture.
 
@@ -13,6 +13,7 @@ import os
 from typing import Any, Callable, Dict, Mapping
 
 from .lfm2 import ConfigError, Lfm2Config
+from .metanex import MetanexConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 _MODEL_TYPES: Dict[str, str] = {}
@@ -33,10 +34,12 @@ def architecture_name(d: Mapping[str, Any]) -> str:
     archs = d.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         name = archs[0]
+    elif isinstance(d.get("architecture"), str):          # some formats name theirs in the singular
+        name = d["architecture"]
     elif d.get("model_type") in _MODEL_TYPES:
         name = _MODEL_TYPES[d["model_type"]]
     else:
-        raise ConfigError("config.json names no architecture: give 'architectures': [name]; "
+        raise ConfigError("config.json names no architecture: give 'architectures': [name] or 'architecture': name; "
                           f"registered: {', '.join(registered_architectures())}")
     if name not in _ARCHITECTURES:
         raise ConfigError(f"unknown architecture {name!r}; registered: {', '.join(registered_architectures())}")
@@ -56,3 +59,4 @@ def load_config(model_dir: str):
 
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config, model_type="lfm2")
+register_architecture("Metanex", MetanexConfig)

@@ -34,11 +34,15 @@ class RopeSpec:
 
     ``pairing`` "adjacent" rotates (2i, 2i+1); "half" rotates (i, i+head_dim/2).
     ``scale`` divides positions before the angle is formed (linear position scaling).
+    ``rotary_dims`` (None: the whole head) rotates only the first that many coordinates of a head:
+    pair i is (i, i + rotary_dims/2) or (2i, 2i+1), its angle pos * theta^(-2i/rotary_dims), and the
+    rest of the head passes unchanged.
     """
     head_dim: int
     theta: float
     pairing: str = "half"
     scale: float = 1.0
+    rotary_dims: Optional[int] = None
     kind: str = "rope"
 
     def __post_init__(self):
@@ -46,6 +50,8 @@ class RopeSpec:
             raise ValueError(f"rope pairing must be 'adjacent' or 'half', got {self.pairing!r}")
         if self.head_dim % 2:
             raise ValueError("rope needs an even head_dim")
+        if self.rotary_dims is not None and (self.rotary_dims % 2 or not 0 <= self.rotary_dims <= self.head_dim):
+            raise ValueError(f"rotary_dims must be even and at most head_dim, got {self.rotary_dims}")
 
 
 @dataclass(frozen=True)
@@ -111,6 +117,119 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class ScalarRMSNormSpec:
+    """y = x * rsqrt(mean(x^2) + eps) * g with ONE gain g for all coordinates (the tensor has no dimensions)."""
+    size: int
+    eps: float
+    kind: str = "rmsnorm_scalar"
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head and no softmax or denominator.
+
+    Per head (key size ``key_dim``, value size ``value_dim``): S_t = decay * S_(t-1) + k_t v_t^T and
+    o_t = S_t^T q_t, with q and k rotated by ``position`` and k scaled by key_dim^(-1/2) after the
+    rotation.  Each head's o is divided by its root mean square (``eps``, no weight), the heads are
+    gated by silu of a fourth projection and projected back.  State per request: S, float32, zero.
+    """
+    hidden: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    position: object
+    eps: float
+    names: Mapping[str, str] = field(default_factory=lambda: _names(q="q", k="k", v="v", gate="g", o="o"))
+    kind: str = "retention"
+
+    def __post_init__(self):
+        if len(self.decay) != self.n_heads:
+            raise ValueError(f"retention: {len(self.decay)} decays for {self.n_heads} heads")
+        if min(self.n_heads, self.key_dim, self.value_dim) < 1:
+            raise ValueError("retention: heads and head sizes must be positive")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention without positions whose keys and values are expanded from one latent per token.
+
+    c_q = rmsnorm(W_dq x) (``q_rank`` wide), q = W_uq c_q;  c = rmsnorm(W_dkv x) (``kv_rank`` wide), per
+    head k = W_uk c and v = W_uv c; only c is cached.  ``window`` None = every earlier key, W = the last W
+    keys with the query's own.  Head h's output is multiplied by sigmoid(W_g x)_h before the output
+    projection.  Both norms have plain weights and ``eps``.
+    """
+    hidden: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    softmax_scale: float
+    eps: float
+    window: Optional[int] = None
+    names: Mapping[str, str] = field(default_factory=lambda: _names(
+        dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv", gate="g", o="o"))
+    kind: str = "latent_attention"
+
+    def __post_init__(self):
+        if self.window is not None and self.window < 1:
+            raise ValueError("attention window must be >= 1")
+        if not (1 <= self.kv_rank <= 256):
+            raise ValueError(f"latent attention: kv_rank must be in [1, 256], got {self.kv_rank}")
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Routed experts: of ``n_experts`` SwiGLU experts of width ``expert_ff`` each token uses the ``top_k``
+    with the largest router logits (float32, with a bias), weighted by the softmax over the chosen logits;
+    a shared expert of width ``shared_ff`` (0: none) runs for every token and is added."""
+    hidden: int
+    n_experts: int
+    top_k: int
+    expert_ff: int
+    shared_ff: int = 0
+    names: Mapping[str, str] = field(default_factory=lambda: _names(
+        expert="e{}", gate="gate", up="up", down="down", router="router", router_bias="router.b", shared="shared"))
+    kind: str = "moe"
+
+    def __post_init__(self):
+        if not (1 <= self.top_k <= self.n_experts):
+            raise ValueError(f"moe: top_k {self.top_k} must be in 1..{self.n_experts}")
+        if self.top_k > 32:
+            raise ValueError("moe: top_k above 32 is not supported")
+
+
+@dataclass(frozen=True)
+class InputConvSpec:
+    """What a sublayer reads, u, is replaced by u + conv(u): a causal convolution over time on each channel,
+    conv(u)_t = sum_j w[:, j] * u_(t - taps + 1 + j), no bias.  State per request: the last taps-1 inputs."""
+    hidden: int
+    taps: int
+    kind: str = "input_conv"
+
+    def __post_init__(self):
+        if not (2 <= self.taps <= 8):
+            raise ValueError(f"input conv taps must be in [2, 8], got {self.taps}")
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself, added after the feed-forward: e = table[token] (``dim`` wide,
+    columns ``offset``..``offset+dim`` of a table shared by all layers), g = gelu_tanh(W_gate x) * e,
+    y = W_proj g, x += rmsnorm(y) * w (plain weight)."""
+    hidden: int
+    dim: int
+    offset: int
+    table_name: str
+    table_width: int
+    vocab_size: int
+    eps: float
+    names: Mapping[str, str] = field(default_factory=lambda: _names(gate="gate", proj="proj", norm="norm"))
+    kind: str = "token_side"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One decoder layer: a block arrangement around a mixer and a feed-forward.
 
@@ -124,6 +243,7 @@ class LayerSpec:
     prefix: str
     names: Mapping[str, str]
     block: str = "prenorm"
+    options: Mapping[str, object] = field(default_factory=dict)   # what a block arrangement has besides the four parts
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,96 @@
+// Routed experts: the router and the weighting of the experts' activations.
+//
+// moe_router: logits z = W_r x + b in float32 (x is the activation row, W_r and b float32); the top_k
+//   experts with the largest logits are chosen (of equal logits the lower index) and weighted by the
+//   softmax over the chosen logits.  Output: dense weights [n_rows, n_experts] float32, zero for the
+//   experts a row does not use.
+// moe_scale: act[row, e*ff + j] *= weights[row, e] for the first n_experts*ff columns of an activation
+//   row of width ld (what lies behind them, a shared expert's columns, stays as it is).  With the
+//   weights applied, one product with all experts' down projections side by side is the weighted sum.
+#include "ng_common.cuh"
+
+#define MOE_MAX_TOP 32
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const T* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
+                  float* __restrict__ weights, int H, int E, int top_k) {
+    extern __shared__ float z[];               // [E]
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const T* xr = x + (size_t)row * H;
+    for (int e = warp; e < E; e += nwarp) {
+        const float* w = wr + (size_t)e * H;
+        float acc = 0.f;
+        for (int i = lane; i < H; i += 32) acc = fmaf(ng_ld(xr + i), w[i], acc);
+        acc = ng_warp_sum(acc);
+        if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
+    }
+    __syncthreads();
+    float* out = weights + (size_t)row * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) out[e] = 0.f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int idx[MOE_MAX_TOP];
+        float val[MOE_MAX_TOP];
+        for (int k = 0; k < top_k; ++k) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e) {
+                const float v = z[e];
+                if (best < 0 || v > bv) {
+                    bool taken = false;
+                    for (int m = 0; m < k; ++m) taken |= idx[m] == e;
+                    if (!taken) { best = e; bv = v; }
+                }
+            }
+            idx[k] = best;
+            val[k] = bv;
+        }
+        float sum = 0.f;
+        const float top = val[0];               // the largest
+        for (int k = 0; k < top_k; ++k) {
+            val[k] = expf(val[k] - top);
+            sum += val[k];
+        }
+        for (int k = 0; k < top_k; ++k) out[idx[k]] = val[k] / sum;
+    }
+}
+
+template <typename T>
+__global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ weights, int n_rows, int E, int ff, int ld) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= E * ff) return;
+    T* p = act + (size_t)row * ld + c;
+    ng_st(p, ng_ld(p) * weights[(size_t)row * E + c / ff]);
+}
+
+NG_EXPORT int ng_moe_router(const void* x, const float* wr, const float* br, float* weights, int n_rows, int H,
+                            int E, int top_k, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (H <= 0 || E <= 0 || top_k < 1 || top_k > E || top_k > MOE_MAX_TOP || E > 8192) return NG_BAD_SIZE;
+    const size_t smem = (size_t)E * sizeof(float);
+    if (act_bf16)
+        NG_LAUNCH((moe_router_kernel<__nv_bfloat16>), n_rows, 128, smem, stream, (const __nv_bfloat16*)x, wr, br, weights,
+                  H, E, top_k);
+    else
+        NG_LAUNCH((moe_router_kernel<float>), n_rows, 128, smem, stream, (const float*)x, wr, br, weights, H, E, top_k);
+    return ng_launch_status();
+}
+
+NG_EXPORT int ng_moe_scale(void* act, const float* weights, int n_rows, int E, int ff, int ld, int act_bf16,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (E <= 0 || ff <= 0 || ld < E * ff || n_rows > 65535) return NG_BAD_SIZE;
+    dim3 grid((E * ff + 255) / 256, n_rows);
+    if (act_bf16)
+        NG_LAUNCH((moe_scale_kernel<__nv_bfloat16>), grid, 256, 0, stream, (__nv_bfloat16*)act, weights, n_rows, E, ff, ld);
+    else
+        NG_LAUNCH((moe_scale_kernel<float>), grid, 256, 0, stream, (float*)act, weights, n_rows, E, ff, ld);
+    return ng_launch_status();
+}

@@ -358,6 +358,117 @@ def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
              float(scale), int(n_splits), int(max_ctx), _slopes(slopes, n_heads), _stream()), "attn_decode_bf16")
 
 
+# ----------------------------------------------------------------------------- input convolution
+def input_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
+               ctx_before: torch.Tensor, slots: torch.Tensor, n_entries: int, max_q: int) -> None:
+    """out[N,H] = u + causal conv of u over time per channel (weight [H, L] float32; tap L-1 is the current
+    token); state[slots, L-1, H] float32 carries each request's last L-1 inputs."""
+    n, H = u.shape
+    L = weight.shape[1]
+    if out.shape != u.shape or out.dtype != u.dtype or weight.shape[0] != H or state.shape[1:] != (L - 1, H):
+        raise KernelError("input_conv: shapes do not fit")
+    _f32(weight, "conv weight"), _f32(state, "conv state")
+    _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
+    f = _fn("input_conv", "ng_input_conv", [_c_void_p] * 7 + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(u), _ptr(weight), _ptr(state), _ptr(out), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries,
+             max_q, H, L, _act_flag(u, "conv input"), _stream()), "input_conv")
+
+
+# ----------------------------------------------------------------------------- retention
+def retention(x: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int, decay: torch.Tensor,
+              state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor,
+              slots: torch.Tensor, n_entries: int, n_heads: int, key_dim: int, value_dim: int, eps: float) -> None:
+    """x[N, 2*nH*(dk+dv)] = q|k|v|g;  per head S = decay*S + k v^T, o = S^T q, out[N, nH*dv] = o/rms(o) * silu(g);
+    state[slots, nH, dk, dv] float32.  q, k rotated on their first ``rot_dims`` coordinates (pairs i, i+rot_dims/2)."""
+    n = x.shape[0]
+    if x.shape[1] != 2 * n_heads * (key_dim + value_dim) or out.shape != (n, n_heads * value_dim) \
+            or out.dtype != x.dtype or state.shape[1:] != (n_heads, key_dim, value_dim) or decay.numel() != n_heads:
+        raise KernelError("retention: shapes do not fit")
+    if rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2):
+        raise KernelError("retention: inv_freq must hold rot_dims/2 frequencies")
+    _f32(inv_freq, "inv_freq"), _f32(decay, "decay"), _f32(state, "retention state")
+    _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
+    f = _fn("retention", "ng_retention", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 4
+            + [_c_float, _c_int, _c_void_p])
+    _check(f(_ptr(x), _ptr(inv_freq), int(rot_dims), _ptr(decay), _ptr(state), _ptr(out), _ptr(cu_q),
+             _ptr(ctx_before), _ptr(slots), n_entries, n_heads, key_dim, value_dim, float(eps),
+             _act_flag(x, "retention input"), _stream()), "retention")
+
+
+# ----------------------------------------------------------------------------- latent attention
+def latent_prep(x: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, cq_out: torch.Tensor, pages: torch.Tensor,
+                gate_out: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor,
+                n_heads: int, eps: float, status: torch.Tensor) -> None:
+    """x[N, rq+rkv+nH] = c_q raw | c raw | gate logits;  cq_out[N, rq] = rmsnorm(c_q raw) * wq;
+    rmsnorm(c raw) * wkv goes to the row's place in pages[P, 1, page, rp] (columns rkv.. zero);
+    gate_out[N, nH] float32 = sigmoid(gate logits)."""
+    n, rq = cq_out.shape
+    rkv = wkv.numel()
+    num_pages, one, page_size, rp = pages.shape
+    if x.shape != (n, rq + rkv + n_heads) or wq.numel() != rq or one != 1 or rp < rkv \
+            or gate_out.shape != (n, n_heads) or cq_out.dtype != x.dtype or pages.dtype != x.dtype:
+        raise KernelError("latent_prep: shapes or dtypes do not fit")
+    _f32(wq, "dq norm"), _f32(wkv, "dkv norm"), _f32(gate_out, "gate")
+    _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
+    f = _fn("latent", "ng_latent_prep", [_c_void_p] * 7 + [_c_int] + [_c_void_p] * 2 + [_c_int] * 7
+            + [_c_float, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(x), _ptr(wq), _ptr(wkv), _ptr(cq_out), _ptr(pages), _ptr(gate_out), _ptr(table), table.shape[1],
+             _ptr(positions), _ptr(row_entry), n, rq, rkv, rp, n_heads, page_size, num_pages, float(eps),
+             _ptr(status), _act_flag(x, "latent input"), _stream()), "latent_prep")
+
+
+def head_gate(y: torch.Tensor, gate: torch.Tensor, n_heads: int) -> None:
+    """y[N, nH*w] *= gate[N, nH] (float32) head by head, in place."""
+    n = y.shape[0]
+    if y.shape[1] % n_heads or gate.shape != (n, n_heads):
+        raise KernelError("head_gate: shapes do not fit")
+    _f32(gate, "gate")
+    f = _fn("latent", "ng_head_gate", [_c_void_p, _c_void_p] + [_c_int] * 4 + [_c_void_p])
+    _check(f(_ptr(y), _ptr(gate), n, n_heads, y.shape[1] // n_heads, _act_flag(y, "head_gate"), _stream()), "head_gate")
+
+
+# ----------------------------------------------------------------------------- routed experts
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], weights: torch.Tensor,
+               top_k: int) -> None:
+    """weights[N, E] float32: softmax over the top_k largest of W_r x + b at the chosen experts, zero elsewhere."""
+    n, H = x.shape
+    E = w_router.shape[0]
+    if w_router.shape != (E, H) or weights.shape != (n, E) or (b_router is not None and b_router.numel() != E):
+        raise KernelError("moe_router: shapes do not fit")
+    _f32(w_router, "router weight"), _f32(b_router, "router bias"), _f32(weights, "routing weights")
+    f = _fn("moe", "ng_moe_router", [_c_void_p] * 4 + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(x), _ptr(w_router), _ptr(b_router), _ptr(weights), n, H, E, int(top_k), _act_flag(x, "router input"),
+             _stream()), "moe_router")
+
+
+def moe_scale(act: torch.Tensor, weights: torch.Tensor, expert_ff: int) -> None:
+    """act[N, ld]: columns e*ff..(e+1)*ff are multiplied by weights[N, e], in place; columns behind E*ff stay."""
+    n, ld = act.shape
+    E = weights.shape[1]
+    if weights.shape[0] != n or ld < E * expert_ff:
+        raise KernelError("moe_scale: shapes do not fit")
+    _f32(weights, "routing weights")
+    f = _fn("moe", "ng_moe_scale", [_c_void_p, _c_void_p] + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(act), _ptr(weights), n, E, int(expert_ff), ld, _act_flag(act, "moe act"), _stream()), "moe_scale")
+
+
+# ----------------------------------------------------------------------------- per-layer token input
+def token_side(h: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor,
+               w_proj: torch.Tensor, w_norm: torch.Tensor, row_entry: torch.Tensor, eps: float,
+               status: torch.Tensor) -> None:
+    """h[N,H] float32 += rmsnorm(W_proj (gelu_tanh(W_gate h) * table[tokens])) * w_norm; all float32."""
+    n, H = h.shape
+    V, dim = table.shape
+    if w_gate.shape != (dim, H) or w_proj.shape != (H, dim) or w_norm.numel() != H:
+        raise KernelError("token_side: shapes do not fit")
+    for t, what in ((h, "residual stream"), (table, "token table"), (w_gate, "gate"), (w_proj, "proj"), (w_norm, "norm")):
+        _f32(t, what)
+    _i32(tokens, "tokens"), _i32(row_entry, "row_entry"), _i32(status, "status")
+    f = _fn("token_side", "ng_token_side", [_c_void_p] * 7 + [_c_int] * 4 + [_c_float, _c_void_p, _c_void_p])
+    _check(f(_ptr(h), _ptr(tokens), _ptr(table), _ptr(w_gate), _ptr(w_proj), _ptr(w_norm), _ptr(row_entry), n, H, dim, V,
+             float(eps), _ptr(status), _stream()), "token_side")
+
+
 # ----------------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
            uniform: Optional[torch.Tensor], out: torch.Tensor, scratch: Optional[torch.Tensor]) -> None:

@@ -119,8 +119,9 @@ class ModelRunner:
         """Device bytes one page id costs over all paged layers (keys and values)."""
         from ..cache.manager import PagedNeed
         esz = torch.empty((), dtype=model.dtype).element_size()
-        return sum(2 * n.n_kv_heads * n.head_dim * page_size * esz
-                   for n in model.cache_needs().values() if isinstance(n, PagedNeed))
+        flat = [n for need in model.cache_needs().values() for n in (need if isinstance(need, tuple) else (need,))]
+        return sum((2 if n.values else 1) * n.n_kv_heads * n.head_dim * page_size * esz
+                   for n in flat if isinstance(n, PagedNeed))
 
     # ------------------------------------------------------------------ requests
     def admit(self, req_id: Hashable) -> int:
@@ -602,15 +603,19 @@ class ModelRunner:
     def _cache_views(self, ctx: StepContext) -> List[object]:
         views = []
         st = self.storage
+
+        def view(lc, writes):
+            if lc.kind == "paged":
+                v = st.v[lc.group]
+                return PagedView(st.k[lc.group][lc.index], v[lc.index] if v is not None else None,
+                                 self._tables[lc.group], writes=writes)
+            if lc.kind == "slot":
+                return SlotView(st.state[lc.group][lc.index])
+            return None
+
         for e in self.model.spec.schedule:
             lc = st.layers[e.cache]
-            if lc.kind == "paged":
-                views.append(PagedView(st.k[lc.group][lc.index], st.v[lc.group][lc.index],
-                                       self._tables[lc.group], writes=e.writes))
-            elif lc.kind == "slot":
-                views.append(SlotView(st.state[lc.group][lc.index]))
-            else:
-                views.append(None)
+            views.append(tuple(view(c, e.writes) for c in lc) if isinstance(lc, tuple) else view(lc, e.writes))
         return views
 
     def check_status(self) -> None:

@@ -42,6 +42,8 @@ class Decoder:
         for layer, block in zip(s.layers, self.blocks):
             for name, decl in block.tensors().items():
                 out[layer.prefix + name] = decl
+            # tensors that belong to no layer but are read by layers (a table every layer takes columns of)
+            out.update(getattr(block, "shared_tensors", dict)())
         for name, decl in self.final_norm.tensors().items():
             out[_join(s.final_norm_name, name)] = decl
         if not s.tie_head:
@@ -59,8 +61,9 @@ class Decoder:
         for layer, block in zip(s.layers, self.blocks):
             pre = layer.prefix
             block.bind({k[len(pre):]: v for k, v in weights.items() if k.startswith(pre)})
-        base = s.final_norm_name[: -len("weight")] if s.final_norm_name.endswith("weight") else s.final_norm_name + "."
-        self.final_norm.bind({k[len(base):]: v for k, v in weights.items() if k.startswith(base)})
+            if hasattr(block, "bind_shared"):
+                block.bind_shared(weights)
+        self.final_norm.bind({rel: weights[_join(s.final_norm_name, rel)] for rel in self.final_norm.tensors()})
 
     def cache_needs(self) -> Dict[int, object]:
         """Cache id -> what the layers that use it need to keep between steps."""
@@ -188,10 +191,14 @@ class _BlockSpec:
         self.mixer, self.ffn = layer.mixer, layer.ffn
         self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm
         self.names = layer.names
+        self.options = layer.options
 
 
 def _join(full_name: str, rel: str) -> str:
     # the final norm's file name is given whole ("model.embedding_norm.weight"): a norm's other tensors stand beside it
+    # a norm whose only tensor has the relative name "" is stored under the given name itself
+    if not rel:
+        return full_name
     if full_name.endswith("weight"):
         return full_name[: -len("weight")] + rel
     return f"{full_name}.{rel}"

@@ -97,6 +97,8 @@ class Attention:
         q = ctx.ws.buf("attn_q", n, s.n_heads * s.head_dim, self.dtype)
         pa = PositionArgs.of(self.position.kernel_args())
         inv_freq, half, pos_scale = pa.inv_freq, pa.half_pairing, pa.pos_scale
+        if pa.rotary_dims is not None and pa.rotary_dims != s.head_dim:
+            raise NotImplementedError("the q/k kernel of this mixer rotates whole heads only")
         if self.owns_cache and not writes:
             # has k/v weights but this run reads another cache: q path only
             if qkv.dim() == 3:

@@ -11,7 +11,8 @@ Interfaces (duck-typed; a part is any class with these members):
              (delta may be None) and ``out`` receives the normed rows in the compute dtype.
 * mixer:     ``cache_need() -> PagedNeed | SlotNeed | None`` and
              ``forward(x, ctx, cache) -> y`` with x, y [N,H]; ``cache`` is a
-             :class:`PagedView`, a :class:`SlotView` or None, matching the declared need.
+             :class:`PagedView`, a :class:`SlotView` or None, matching the declared need
+             (a block that declares a tuple of needs is handed a tuple of views).
 * ffn:       ``forward(x, ctx) -> y`` with x, y [N,H].
              A mixer or ffn may return, instead of y, a float32 stack [S,N,H] whose sum over S
              is y (split-K partial sums); the norm that follows adds it up.  When
@@ -94,6 +95,7 @@ class PositionArgs:
     half_pairing: bool = False
     pos_scale: float = 1.0
     score_slopes: Optional[torch.Tensor] = None
+    rotary_dims: Optional[int] = None      # a partial rotation: only the first that many coordinates of a head
 
     @classmethod
     def of(cls, args) -> "PositionArgs":
@@ -105,7 +107,7 @@ class PagedView:
     """One layer's keys and values, [pages, n_kv_heads, page_size, head_dim] each, and the
     step's block table [R, max_pages] (entry-indexed; -1 = no page)."""
     k_pages: torch.Tensor
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]      # None for pages without a value half
     table: torch.Tensor
     writes: bool = True          # False: this run of the layer reads another layer's cache
 

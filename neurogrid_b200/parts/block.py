@@ -61,3 +61,92 @@ class PreNormBlock:
         m = self.mixer.forward(x, ctx, cache)
         x = self.ffn_norm.forward(h, m, buf)
         return self.ffn.forward(x, ctx)
+
+
+@register("block", "prenorm_conv_side")
+class PreNormConvSideBlock:
+    """Pre-norm with an input convolution in front of each sublayer and a token input behind the layer:
+
+        u = norm1(x);  x += mixer(u + conv1(u));  u = norm2(x);  x += ffn(u + conv2(u));  x += side(x, token)
+
+    ``spec.options``: ``input_conv`` (an InputConvSpec, or None: sublayers read the norm's output) and
+    ``token_side`` (a TokenSideSpec or None).  ``spec.ffn`` None: the layer has no feed-forward (and no second
+    norm or convolution).  The block keeps, per request, the mixer's cache and each convolution's last inputs:
+    it declares a tuple of needs and is handed the views in the same order (mixer, conv1, conv2)."""
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        from .input_conv import InputConv, TokenSide
+        self.spec, self.dtype = spec, dtype
+        kw = dict(dtype=dtype, device=device)
+        opt = spec.options
+        self.mixer = registry.build("mixer", spec.mixer, **kw)
+        self.mixer_norm = registry.build("norm", spec.mixer_norm, **kw)
+        self.ffn = registry.build("ffn", spec.ffn, **kw) if spec.ffn is not None else None
+        self.ffn_norm = registry.build("norm", spec.ffn_norm, **kw) if spec.ffn is not None else None
+        conv = opt.get("input_conv")
+        self.mixer_conv = InputConv(conv, **kw) if conv is not None else None
+        self.ffn_conv = InputConv(conv, **kw) if conv is not None and self.ffn is not None else None
+        self.side = TokenSide(opt["token_side"], **kw) if opt.get("token_side") is not None else None
+
+    def parts(self):
+        n = self.spec.names
+        roles = {"mixer": self.mixer, "ffn": self.ffn, "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm,
+                 "mixer_conv": self.mixer_conv, "ffn_conv": self.ffn_conv, "side": self.side}
+        return {n[r]: p for r, p in roles.items() if p is not None}
+
+    def tensors(self):
+        out = {}
+        for sub, part in self.parts().items():
+            for name, decl in part.tensors().items():
+                out[f"{sub}.{name}" if name else sub] = decl
+        return out
+
+    def shared_tensors(self):
+        return self.side.shared_tensors() if self.side is not None else {}
+
+    def bind(self, t):
+        for sub, part in self.parts().items():
+            pre = sub + "."
+            own = {k[len(pre):]: v for k, v in t.items() if k.startswith(pre)}
+            if sub in t:
+                own[""] = t[sub]
+            part.bind(own)
+
+    def bind_shared(self, weights):
+        if self.side is not None:
+            self.side.bind_shared(weights)
+
+    def cache_need(self):
+        needs = [self.mixer.cache_need()]
+        needs += [c.cache_need() for c in (self.mixer_conv, self.ffn_conv) if c is not None]
+        return tuple(needs)
+
+    def kernels(self):
+        return [job for p in self.parts().values() for job in getattr(p, "kernels", list)()]
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in self.parts().values())
+
+    def forward(self, h, pending, ctx, cache):
+        from ..csrc import ops
+        n, H = h.shape
+        views = list(cache)
+        mixer_cache = views.pop(0)
+        buf = ctx.ws.buf("normed", n, H, self.dtype)
+        ctx.residual = h if ctx.fuse_residual else None
+        x = self.mixer_norm.forward(h, pending, buf)
+        if self.mixer_conv is not None:
+            x = self.mixer_conv.forward(x, ctx, views.pop(0), ctx.ws.buf("conv_out", n, H, self.dtype))
+        out = self.mixer.forward(x, ctx, mixer_cache)
+        if self.ffn is not None:
+            x = self.ffn_norm.forward(h, out, buf)
+            if self.ffn_conv is not None:
+                x = self.ffn_conv.forward(x, ctx, views.pop(0), ctx.ws.buf("conv_out", n, H, self.dtype))
+            out = self.ffn.forward(x, ctx)
+        if self.side is None:
+            return out
+        if out is not None:
+            ops.residual_add(h, out)              # the token input reads the complete stream
+        self.side.forward(h, ctx)
+        return None

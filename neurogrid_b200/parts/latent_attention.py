@@ -1,0 +1,86 @@
+"""Latent attention: softmax attention whose keys and values are expanded from one cached latent per token."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import PagedNeed
+from ..csrc import ops
+from ..weights.decl import TensorDecl
+from .registry import register
+
+
+@register("mixer", "latent_attention")
+class LatentAttention:
+    """c_q = rmsnorm(W_dq x), q_h = W_uq,h c_q;  c = rmsnorm(W_dkv x), k_h = W_uk,h c, v_h = W_uv,h c;
+    out = W_o concat_h( sigmoid(W_g x)_h * softmax(q_h k_h^T * scale) v_h ) over a window; no positions.
+
+    Only c is cached (pages without a value half, one "head" of kv_rank columns, padded to a multiple
+    of 16 with zeros).  The expansions are folded into the neighbouring matrices when the weights are
+    bound (in float64, rounded once to the compute dtype):
+        q_h . k_h = (W_uk,h^T W_uq,h c_q) . c        -> one matrix [heads * rank, q_rank] makes the queries
+        W_o,h (g_h * W_uv,h sum_j p_j c_j)           -> one matrix [hidden, heads * rank] ends the mixer
+    so the attention core is a multi-query attention in which every head reads the latent pages both as
+    keys and as values.  Scores, softmax weights and their sum with the values are float32 (the
+    order-fixed kernel, one warp per row and head), as are the two norms and the gate."""
+
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        if not owns_cache:
+            raise ValueError("a latent attention layer keeps its own cache")
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.rank_p = -(-spec.kv_rank // 16) * 16
+        self.w_down = self.w_q = self.w_out = self.dq_norm = self.dkv_norm = None
+
+    def tensors(self):
+        s, n = self.spec, self.spec.names
+        return {n["dq"]: TensorDecl((s.q_rank, s.hidden)), n["dq_norm"]: TensorDecl((s.q_rank,), "norm"),
+                n["uq"]: TensorDecl((s.n_heads * s.key_dim, s.q_rank)),
+                n["dkv"]: TensorDecl((s.kv_rank, s.hidden)), n["dkv_norm"]: TensorDecl((s.kv_rank,), "norm"),
+                n["uk"]: TensorDecl((s.n_heads * s.key_dim, s.kv_rank)),
+                n["uv"]: TensorDecl((s.n_heads * s.value_dim, s.kv_rank)),
+                n["gate"]: TensorDecl((s.n_heads, s.hidden)),
+                n["o"]: TensorDecl((s.hidden, s.n_heads * s.value_dim))}
+
+    def bind(self, t):
+        s, n = self.spec, self.spec.names
+        kw = dict(device=self.device, dtype=self.dtype)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        H, rp = s.n_heads, self.rank_p
+        self.w_down = torch.cat([t[n[p]].to(**kw) for p in ("dq", "dkv", "gate")]).contiguous()
+        self.dq_norm = t[n["dq_norm"]].to(**f32).contiguous()
+        self.dkv_norm = t[n["dkv_norm"]].to(**f32).contiguous()
+        uq = t[n["uq"]].double().view(H, s.key_dim, s.q_rank)
+        uk = t[n["uk"]].double().view(H, s.key_dim, s.kv_rank)
+        uv = t[n["uv"]].double().view(H, s.value_dim, s.kv_rank)
+        wo = t[n["o"]].double().view(s.hidden, H, s.value_dim)
+        wq = torch.zeros(H, rp, s.q_rank, dtype=torch.float64)
+        wq[:, :s.kv_rank] = torch.einsum("hdr,hdq->hrq", uk, uq)
+        wout = torch.zeros(s.hidden, H, rp, dtype=torch.float64)
+        wout[:, :, :s.kv_rank] = torch.einsum("ohv,hvr->ohr", wo, uv)
+        self.w_q = wq.view(H * rp, s.q_rank).to(**kw).contiguous()
+        self.w_out = wout.view(s.hidden, H * rp).to(**kw).contiguous()
+
+    def cache_need(self):
+        return PagedNeed(1, self.rank_p, self.spec.window, values=False)
+
+    def kernels(self):
+        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("latent", None),
+                ("attention_generic", None)]
+
+    def forward(self, x, ctx, cache):
+        s = self.spec
+        n, H, rp = x.shape[0], s.n_heads, self.rank_p
+        down = ctx.ws.buf("lat_down", n, self.w_down.shape[0], self.dtype)
+        ops.linear(x, self.w_down, None, down)
+        cq = ctx.ws.buf("lat_cq", n, s.q_rank, self.dtype)
+        gate = ctx.ws.buf("lat_gate", n, H, torch.float32)
+        ops.latent_prep(down, self.dq_norm, self.dkv_norm, cq, cache.k_pages, gate, cache.table, ctx.positions,
+                        ctx.row_entry, H, s.eps, ctx.status)
+        q = ctx.ws.buf("lat_q", n, H * rp, self.dtype)
+        ops.linear(cq, self.w_q, None, q)
+        o = ctx.ws.buf("lat_o", n, H * rp, self.dtype)
+        ops.attention_generic(q, cache.k_pages, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, o,
+                              H, s.window, s.softmax_scale)
+        ops.head_gate(o, gate, H)
+        return ops.linear_to_residual(o, self.w_out, None, ctx.ws, "mixer_out", residual=ctx.residual)

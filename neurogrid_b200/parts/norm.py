@@ -33,3 +33,17 @@ class RMSNorm:
     def forward(self, h, delta, out, rows=None):
         ops.add_rmsnorm(h, delta, self.weight, out, self.spec.eps, rows)
         return out
+
+
+@register("norm", "rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """y = x * rsqrt(mean(x^2) + eps) * g with one gain g for all coordinates.  The gain's tensor has no
+    dimensions and the relative name "": it is stored under the norm's own name.  It is spread to a
+    vector when bound, so the kernel of :class:`RMSNorm` (residual sum in front, float32 throughout) serves."""
+
+    def tensors(self):
+        return {"": TensorDecl((), "norm")}
+
+    def bind(self, t):
+        g = t[""].to(device=self.device, dtype=torch.float32).reshape(1)
+        self.weight = g.expand(self.spec.size).contiguous()

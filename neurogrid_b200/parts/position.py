@@ -9,7 +9,8 @@ from .registry import register
 
 @register("position", "rope")
 class Rope:
-    """angle(pos, i) = (pos / scale) * theta^(-2i/head_dim); pairs (2i, 2i+1) or (i, i+hd/2).
+    """angle(pos, i) = (pos / scale) * theta^(-2i/dims); pairs (2i, 2i+1) or (i, i+dims/2), dims = the head's
+    size or, for a partial rotation, ``rotary_dims`` (the frequency table then has rotary_dims/2 entries).
 
     Reference: gpu/cuda/bf16_utils.cu:330-378.  The frequencies are formed in float64 on the
     host and rounded once; the angle and its sine and cosine are float32 on the device.
@@ -17,11 +18,13 @@ class Rope:
 
     def __init__(self, spec, *, device):
         self.spec = spec
-        i = torch.arange(spec.head_dim // 2, dtype=torch.float64)
-        self.inv_freq = (float(spec.theta) ** (-2.0 * i / spec.head_dim)).to(torch.float32).to(device)
+        dims = spec.head_dim if spec.rotary_dims is None else spec.rotary_dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        self.inv_freq = (float(spec.theta) ** (-2.0 * i / max(dims, 1))).to(torch.float32).to(device)
 
     def kernel_args(self):
-        return PositionArgs(self.inv_freq, self.spec.pairing == "half", float(self.spec.scale))
+        return PositionArgs(self.inv_freq, self.spec.pairing == "half", float(self.spec.scale),
+                            rotary_dims=self.spec.rotary_dims)
 
 
 @register("position", "none")
