@@ -103,6 +103,10 @@ static inline void ng_launch(void (*kernel)(KP...), dim3 grid, dim3 block, size_
 }
 #define NG_LAUNCH(kernel, grid, block, smem, stream, ...) ng_launch((kernel), dim3(grid), dim3(block), (smem), (stream), __VA_ARGS__)
 
+#include <cstdio>
 static inline int ng_launch_status() {
-    return cudaGetLastError() == cudaSuccess ? NG_OK : NG_LAUNCH_FAILED;
+    const cudaError_t err = cudaGetLastError();
+    if (err == cudaSuccess) return NG_OK;
+    fprintf(stderr, "[neurogrid_b200] a kernel launch failed: %s\n", cudaGetErrorString(err));   // the caller raises
+    return NG_LAUNCH_FAILED;
 }

@@ -36,3 +36,16 @@ def model_dirs(tmp_path_factory):
         write_random_model(cfg, seed, str(d))
         out[name] = str(d)
     return out
+
+
+@pytest.fixture(scope="session")
+def metanex_dirs(tmp_path_factory):
+    """Model folders for the tiny Metanex configurations; "<name>_calm" has routers that hardly look at the
+    token, for comparisons in bfloat16."""
+    import metanex_models
+    out = {}
+    for name, (cfg, seed) in metanex_models.CONFIGS.items():
+        out[name] = metanex_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"metanex_{name}")))
+        out[name + "_calm"] = metanex_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"metanex_{name}c")),
+                                                         router_gain=0.05)
+    return out

@@ -62,14 +62,24 @@ def rotate_half(x, pos, dims, base):
     return out
 
 
-def retention(h, w, pre, m, eps):
-    """Linear attention with a fixed decay per head: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t."""
+def bf16(t):
+    """Round to bfloat16 and back: what a matrix product of the bfloat16 path hands on."""
+    return t.to(torch.bfloat16).to(F64)
+
+
+def same(t):
+    return t
+
+
+def retention(h, w, pre, m, eps, rnd=same):
+    """Linear attention with a fixed decay per head: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.
+    ``rnd`` rounds what the projections hand on (the identity, or ``bf16``)."""
     T = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
     rot = m.get("rot") or {}
-    q = (h @ w[pre + "q"].T).view(T, H, dk)
-    k = (h @ w[pre + "k"].T).view(T, H, dk)
-    v = (h @ w[pre + "v"].T).view(T, H, dv)
+    q = rnd(h @ w[pre + "q"].T).view(T, H, dk)
+    k = rnd(h @ w[pre + "k"].T).view(T, H, dk)
+    v = rnd(h @ w[pre + "v"].T).view(T, H, dv)
     pos = torch.arange(T)
     q = rotate_half(q, pos, int(rot.get("dims", 0)), float(rot.get("base", 1.0)))
     k = rotate_half(k, pos, int(rot.get("dims", 0)), float(rot.get("base", 1.0))) * dk ** -0.5
@@ -80,7 +90,7 @@ def retention(h, w, pre, m, eps):
         S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hkv,hk->hv", S, q[t])
     o = rms(o, eps).reshape(T, H * dv)
-    return (o * silu(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    return rnd(o * silu(rnd(h @ w[pre + "g"].T))) @ w[pre + "o"].T
 
 
 def latent_attention(h, w, pre, m, eps):
@@ -92,7 +102,7 @@ def latent_attention(h, w, pre, m, eps):
     c = rms(h @ w[pre + "dkv"].T, eps) * w[pre + "dkv.norm"]
     k = (c @ w[pre + "uk"].T).view(T, H, dk)
     v = (c @ w[pre + "uv"].T).view(T, H, dv)
-    win = int(m["mask"]["size"])
+    win = int(m["mask"]["size"]) if m.get("mask") else T          # no mask: every earlier key
     out = torch.zeros(T, H, dv, dtype=F64)
     for t in range(T):
         lo = max(0, t - win + 1)
