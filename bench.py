@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the LFM2-1.2B shape, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m]
+                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex]
 
 A "step" is one decode step of the batch.  The default run has the layer sizes of the
 LFM2-1.2B configuration, a batch of 8 and requests that hold 2,048-token prompts and grow
@@ -579,6 +579,201 @@ def run_workload(args):
                       "clocks": clocks.summary(), "impl": "ours"}))
 
 
+# ---------------------------------------------------------------------------------------------- --workload metanex
+def metanex_config(width, layers):
+    """A Metanex configuration with layers of a real model's sizes: three retention layers to one latent
+    attention layer, routed experts whose widths add up to about four times the model's, a shared expert."""
+    heads = width // 128
+    ret = {"type": "retention", "mixer": {"heads": heads, "dim": 128, "vdim": 128,
+                                          "decay": [1.0 - 2.0 ** (-5 - 6 * h / max(1, heads - 1)) for h in range(heads)],
+                                          "rot": {"dims": 64, "base": 1000000.0}}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "q_rank": 768, "kv_rank": 128,
+                                                 "scale": 128 ** -0.5, "mask": {"size": 1024}}}
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 4}, "expert": {"ff": width // 4}, "shared": {"ff": width // 2}}
+    pattern = [ret, ret, lat, ret]
+    return {"architecture": "Metanex", "vocab": 65536, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "token_side": {"dim": 64},
+            "layers": [dict(pattern[i % 4], mlp=mlp) for i in range(layers)]}
+
+
+def run_metanex(args):
+    """Prefill and decode throughput of the Metanex design at layer sizes of a real model, beside LFM2 (the closest
+    existing model: a hybrid of state layers and attention layers) at equal width and depth, and the design's own
+    kernels one by one with what they must move or compute.  One JSON line.  Random weights, synthetic token ids;
+    CUDA events; the L2 is flushed between timed steps."""
+    import torch
+    from neurogrid_b200 import Engine
+    from neurogrid_b200.engine import StepEntry
+    pk = peaks()
+    l2 = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda:0")
+    clocks = ClockSampler(0)
+    clocks.start()
+    results = []
+    for width, layers in ((1024, 16), (2048, 16)):
+        lfm2 = dict(LFM2_1_2B)
+        lfm2.update(SHAPES["350m" if width == 1024 else "1.2b"])
+        arms = {"metanex": metanex_config(width, layers), "lfm2": lfm2}
+        row = {"width": width, "layers": layers}
+        for arm, cfg in arms.items():
+            eng = Engine(config=cfg, random_weights=0, dtype="bf16", max_seq_len=8192, max_requests=8,
+                         max_tokens_per_step=2048, num_pages=8 * 4096 // 16)
+            r = eng.runner
+            V = eng.model.spec.vocab_size
+            g = torch.Generator().manual_seed(1)
+            toks = lambda n: torch.randint(0, V, (n,), generator=g).tolist()
+
+            def timed(fn, reps):
+                ts = []
+                for _ in range(reps):
+                    flush_l2(l2)
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    fn()
+                    b.record()
+                    torch.cuda.synchronize()
+                    ts.append(a.elapsed_time(b))
+                return median(ts)
+
+            # prefill: one request's 2,048-token prompt in one step (the third meeting of the shape replays its graph)
+            n_pre = [0]
+
+            def prefill():
+                rid = ("p", n_pre[0])
+                n_pre[0] += 1
+                r.step([StepEntry(rid, toks(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+                r.finish(rid)
+
+            for _ in range(3):
+                prefill()
+            torch.cuda.synchronize()
+            ms = timed(prefill, 5)
+            row[arm + "_prefill_ms"] = round(ms, 3)
+            row[arm + "_prefill_tok_s"] = round(PREFILL_TOKENS / ms * 1e3)
+            # decode: 8 requests (and 1) that hold 2,048 tokens each, one token a step
+            for i in range(8):
+                r.step([StepEntry(("d", i), toks(PREFILL_TOKENS), [])])
+            for batch in (8, 1):
+                step = lambda: r.step([StepEntry(("d", i), toks(1), [0]) for i in range(batch)])
+                for _ in range(max(3, args.warmup)):
+                    step()
+                torch.cuda.synchronize()
+                ms = timed(step, 24)
+                row[f"{arm}_decode{batch}_ms"] = round(ms, 4)
+                row[f"{arm}_decode{batch}_tok_s"] = round(batch / ms * 1e3)
+            r.check_status()
+            row[arm + "_weights_gb"] = round(eng.model.weight_bytes() / 1e9, 3)
+            if arm == "metanex" and not args.no_kernels:
+                row["kernels"] = metanex_kernel_times(eng, l2, pk)
+            del eng, r
+            torch.cuda.empty_cache()
+        results.append(row)
+    time.sleep(0.06)
+    clocks.stop()
+    print(json.dumps({"workload": "metanex", "what": "Metanex beside LFM2 at equal width and depth: prefill of 2,048 tokens, "
+                      "decode at batch 8 and 1 after 2,048 tokens", "results": results, "dtype": "bf16",
+                      "data": "synthetic token ids, random-init weights", "peaks": pk, "clocks": clocks.summary(),
+                      "impl": "ours"}))
+
+
+def metanex_kernel_times(eng, l2, pk):
+    """The design's own kernels alone (CUDA events around one launch, L2 flushed before it, median of 7), with the
+    bytes each must move and the float32 operations it must do: microseconds, and the fraction of the measured copy
+    bandwidth (or, for the chunked retention, of the float32 FFMA rate of the SMs at the clock seen)."""
+    import torch
+    from neurogrid_b200.csrc import ops
+    from neurogrid_b200.parts.base import Workspace
+    from neurogrid_b200.parts import PagedView, SlotView, StepContext
+    model, dev = eng.model, eng.device
+    D = model.spec.hidden
+    ret = next(b.mixer for b in model.blocks if type(b.mixer).__name__ == "Retention")
+    lat = next(b.mixer for b in model.blocks if type(b.mixer).__name__ == "LatentAttention")
+    blk = model.blocks[0]
+    g = torch.Generator(device=dev).manual_seed(3)
+    rnd = lambda *s: (torch.randn(*s, generator=g, device=dev)).to(torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for _ in range(9):
+            flush_l2(l2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return median(ts[2:])
+
+    out = {"unit": "us"}
+    bw = pk["hbm_gbs"] * 1e9
+
+    def mem(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "of_copy_bandwidth": round(nbytes / (us * 1e-6) / bw, 3)}
+
+    for rows, entries in ((PREFILL_TOKENS, 1), (8, 8)):
+        tag = "prefill" if entries == 1 else "decode8"
+        q = rows // entries
+        cu, cb, sl = i32([q * e for e in range(entries + 1)]), i32([2048] * entries), i32(list(range(entries)))
+        pos = i32([2048 + t for e in range(entries) for t in range(q)])
+        re = i32([e for e in range(entries) for _ in range(q)])
+        # input convolution
+        u, o = rnd(rows, D), torch.empty(rows, D, dtype=torch.bfloat16, device=dev)
+        st = torch.zeros(8, blk.mixer_conv.spec.taps - 1, D, device=dev)
+        us = timed(lambda: ops.input_conv(u, blk.mixer_conv.weight, st, o, cu, cb, sl, entries, q))
+        mem(f"{tag}_input_conv", us, 2 * rows * D * 2 + 2 * entries * st[0].numel() * 4)
+        # retention
+        s = ret.spec
+        x = rnd(rows, ret.w_in.shape[0])
+        ro = torch.empty(rows, s.n_heads * s.value_dim, dtype=torch.bfloat16, device=dev)
+        state = torch.zeros(8, s.n_heads, s.key_dim, s.value_dim, device=dev)
+        chunked = q >= ret.CHUNKED_MIN_ROWS
+        us = timed(lambda: ops.retention(x, ret.position.inv_freq, s.position.rotary_dims, ret.decay, state, ro, cu, cb, sl,
+                                         entries, s.n_heads, s.key_dim, s.value_dim, s.eps, chunked=chunked))
+        nbytes = x.numel() * 2 + ro.numel() * 2 + 2 * entries * state[0].numel() * 4
+        mem(f"{tag}_retention", us, nbytes)
+        if chunked:
+            C = 32
+            flops = 2 * rows * s.n_heads * (s.key_dim * (C + 1) / 2 + s.value_dim * (C + 1) / 2 + 2 * s.key_dim * s.value_dim)
+            out[f"{tag}_retention"]["fp32_flops"] = int(flops)
+            out[f"{tag}_retention"]["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
+        # token input
+        h = torch.randn(rows, D, generator=g, device=dev)
+        tok = torch.randint(0, model.spec.vocab_size, (rows,), generator=g, device=dev).to(torch.int32)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        sd = blk.side
+        us = timed(lambda: ops.token_side(h, tok, sd.table, sd.w_gate, sd.w_proj, sd.w_norm, re, sd.spec.eps, status))
+        mem(f"{tag}_token_side", us, 2 * rows * D * 4 + (sd.w_gate.numel() + sd.w_proj.numel()) * 4)
+        # router and weighting of the experts' activations
+        f = blk.ffn
+        xs, wts = rnd(rows, D), torch.empty(rows, f.spec.n_experts, device=dev)
+        us = timed(lambda: ops.moe_router(xs, f.w_router, f.b_router, wts, f.spec.top_k))
+        mem(f"{tag}_moe_router", us, rows * D * 2 + f.w_router.numel() * 4 + wts.numel() * 4)
+        act = rnd(rows, f.width)
+        us = timed(lambda: ops.moe_scale(act, wts, f.spec.expert_ff))
+        mem(f"{tag}_moe_scale", us, 2 * rows * f.spec.n_experts * f.spec.expert_ff * 2)
+        # latent attention: norms + cache write + gate, then the attention core over the latent pages
+        ls = lat.spec
+        ps, n_pages = 16, 8 * 4096 // 16
+        pages = rnd(n_pages, 1, ps, lat.rank_p)
+        table = torch.arange(entries * 256, dtype=torch.int32, device=dev).view(entries, 256)
+        down = rnd(rows, lat.w_down.shape[0])
+        cq = torch.empty(rows, ls.q_rank, dtype=torch.bfloat16, device=dev)
+        gate = torch.empty(rows, ls.n_heads, device=dev)
+        us = timed(lambda: ops.latent_prep(down, lat.dq_norm, lat.dkv_norm, cq, pages, gate, table, pos, re, ls.n_heads,
+                                           ls.eps, status))
+        mem(f"{tag}_latent_prep", us, down.numel() * 2 + cq.numel() * 2 + rows * lat.rank_p * 2 + gate.numel() * 4)
+        qa = rnd(rows, ls.n_heads * lat.rank_p)
+        ao = torch.empty_like(qa)
+        us = timed(lambda: ops.latent_core(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale))
+        keys = min(ls.window, 2048 + q)
+        flops = 4 * rows * ls.n_heads * keys * lat.rank_p
+        out[f"{tag}_latent_attention_core"] = {"us": round(us, 2), "fp32_flops": int(flops),
+                                               "tflops": round(flops / (us * 1e-6) / 1e12, 2),
+                                               "bytes": int(2 * qa.numel() * 2 + entries * keys * lat.rank_p * 2)}
+    return out
+
+
+
 def run_reference(args):
     """The reference's own library through its stock entry points; same metric, same line."""
     shape_name = SHAPE_NAMES[args.shape]
@@ -641,8 +836,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="tokens each request holds before decoding (default 2,048; the context is twice this)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m"],
-                    help="run another workload of the benchmark set through Engine.generate instead")
+    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex"],
+                    help="run another workload of the benchmark set through Engine.generate instead; metanex: the "
+                         "Metanex design beside LFM2 at equal width and depth, prefill and decode, and its kernels alone")
     ap.add_argument("--repeat", type=int, default=2, help="--workload: runs (the first also warms up and captures graphs)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel timings")
     ap.add_argument("--profile-only", action="store_true",
@@ -657,6 +853,9 @@ def main():
         return 0
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "metanex":
+        run_metanex(args)
+        return 0
     if args.workload:
         run_workload(args)
         return 0

@@ -1,7 +1,8 @@
 """neurogrid_b200: a small, whole inference engine for one B200, built from parts.
 
-One architecture is registered (``Lfm2ForCausalLM``: gated short-convolution layers
-interleaved with grouped-query attention).  The public entry points are
+Two architectures are registered: ``Lfm2ForCausalLM`` (gated short-convolution layers
+interleaved with grouped-query attention) and ``Metanex`` (retention and latent-attention layers
+with routed experts).  The public entry points are
 :class:`neurogrid_b200.Engine` (generate), ``bin/neurogrid`` (command line) and
 ``bin/trace_run`` (token-by-token replay that writes logits).
 """

@@ -17,7 +17,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="neurogrid", description="LFM2 inference on one B200 (token ids in, token ids out)")
+    ap = argparse.ArgumentParser(prog="neurogrid", description="LFM2 and Metanex inference on one B200 (token ids in, token ids out)")
     a = ap.add_argument
     a("-model", "--model", default="", help="Path to model weights (folder with config.json and safetensors)")
     a("-gpu", "--gpu", type=int, default=0, help="Local GPU device ID")

@@ -7,7 +7,7 @@
 //   gate = sigmoid(gate logits)                             -> gate_out [n_rows, nH]    (float32)
 // Both norms and the gate are float32; only what a matrix product or the cache reads is rounded.
 //
-// head_gate: y[row, h, :] *= gate[row, h] for rows of [n_rows, nH * width].
+// head_gate: y[row, h, :] *= gate[row, h] for rows of [n_rows, nH * width] (for a core that does not gate itself).
 #include "ng_common.cuh"
 
 template <typename T>
@@ -60,6 +60,132 @@ __global__ void head_gate_kernel(T* __restrict__ y, const float* __restrict__ ga
     if (i >= total) return;
     const size_t rh = i / width;              // row * nH + head
     ng_st(y + i, ng_ld(y + i) * gate[rh]);
+}
+
+// latent_core: the attention core over the latent pages.  Every head of a row reads the same latent both as
+// key and as value (the expansions to per-head keys and values are folded into the matrices around the core),
+// so a block takes one row, stages the row's visible latents tile by tile (32 keys, float32) in shared memory
+// once for all heads, and each warp runs the online softmax of its heads over the tile: a lane per key for the
+// scores, a lane per column for the weighted sum.  Scores, weights and sums are float32; keys are walked in
+// ascending order from the window's first key, so a row's result does not depend on the cut or the batch.
+// The head's gate multiplies the result before it is stored.
+#define LC_TILE 32
+#define LC_MAX_J 8       // columns per lane: rank <= 256
+
+template <typename T, int HPW>
+__global__ void __launch_bounds__(512)
+latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const int* __restrict__ table, int table_stride,
+                   const int* __restrict__ positions, const int* __restrict__ row_entry, const float* __restrict__ gate,
+                   T* __restrict__ out, int nH, int rp, int page_size, int num_pages, int window, float scale) {
+    extern __shared__ float sm[];
+    const int ldt = rp + 1;
+    float* Ts = sm;                        // [LC_TILE][rp+1]
+    float* qs = sm + LC_TILE * ldt;        // [nH][rp], scaled
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const int entry = row_entry[row];
+    T* orow = out + (size_t)row * nH * rp;
+    if (entry < 0) {
+        for (int i = tid; i < nH * rp; i += blockDim.x) ng_st(orow + i, 0.f);
+        return;
+    }
+    const int pos = positions[row];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* trow = table + (size_t)entry * table_stride;
+    for (int i = tid; i < nH * rp; i += blockDim.x) qs[i] = ng_ld(q + (size_t)row * nH * rp + i) * scale;
+    float m[HPW], l[HPW], acc[HPW][LC_MAX_J];
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        m[u] = -INFINITY;
+        l[u] = 0.f;
+#pragma unroll
+        for (int j = 0; j < LC_MAX_J; ++j) acc[u][j] = 0.f;
+    }
+    for (int k0 = lo; k0 <= pos; k0 += LC_TILE) {
+        const int n = min(LC_TILE, pos + 1 - k0);
+        __syncthreads();
+        for (int idx = tid; idx < n * rp; idx += blockDim.x) {
+            const int k = idx / rp, d = idx % rp;
+            const int kp = k0 + k;
+            const int page = trow[kp / page_size];
+            float v = 0.f;
+            if (page >= 0 && page < num_pages) v = ng_ld(pages + ((size_t)page * page_size + (kp % page_size)) * rp + d);
+            Ts[k * ldt + d] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < HPW; ++u) {
+            const int head = warp + u * nwarp;
+            if (head >= nH) break;
+            const float* qh = qs + (size_t)head * rp;
+            float s = 0.f;
+            if (lane < n) {
+                const float* tk = Ts + lane * ldt;
+                for (int d = 0; d < rp; ++d) s = fmaf(qh[d], tk[d], s);
+            } else {
+                s = -INFINITY;
+            }
+            const float m_new = fmaxf(m[u], ng_warp_max(s));
+            const float corr = expf(m[u] - m_new);
+            const float p = lane < n ? expf(s - m_new) : 0.f;
+            l[u] = l[u] * corr + ng_warp_sum(p);
+            m[u] = m_new;
+#pragma unroll
+            for (int j = 0; j < LC_MAX_J; ++j) acc[u][j] *= corr;
+            for (int k = 0; k < n; ++k) {
+                const float pk = __shfl_sync(0xffffffffu, p, k);
+                const float* tk = Ts + k * ldt;
+#pragma unroll
+                for (int j = 0; j < LC_MAX_J; ++j) {
+                    const int d = lane + 32 * j;
+                    if (d < rp) acc[u][j] = fmaf(pk, tk[d], acc[u][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int head = warp + u * nwarp;
+        if (head >= nH) break;
+        const float f = (l[u] > 0.f ? 1.f / l[u] : 0.f) * (gate ? gate[(size_t)row * nH + head] : 1.f);
+#pragma unroll
+        for (int j = 0; j < LC_MAX_J; ++j) {
+            const int d = lane + 32 * j;
+            if (d < rp) ng_st(orow + (size_t)head * rp + d, acc[u][j] * f);
+        }
+    }
+}
+
+// q, out: [n_rows, nH*rp]; pages: [num_pages, 1, page_size, rp]; gate: float32 [n_rows, nH] or null.
+NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table, int table_stride, const int* positions,
+                             const int* row_entry, const float* gate, void* out, int n_rows, int nH, int rp, int page_size,
+                             int num_pages, int window, float scale, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (nH <= 0 || rp <= 0 || rp > 32 * LC_MAX_J || page_size <= 0 || nH > 64) return NG_BAD_SIZE;
+    const int nwarp = nH <= 16 ? nH : 16;
+    const int hpw = (nH + nwarp - 1) / nwarp;
+    const size_t smem = ((size_t)LC_TILE * (rp + 1) + (size_t)nH * rp) * sizeof(float);
+    if (smem > 200 * 1024) return NG_BAD_SIZE;
+#define LC_LAUNCH(TT, HH)                                                                                              \
+    {                                                                                                                  \
+        static bool configured = false;                                                                                \
+        if (!configured) {                                                                                             \
+            if (cudaFuncSetAttribute(latent_core_kernel<TT, HH>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                     200 * 1024) != cudaSuccess)                                                       \
+                return NG_LAUNCH_FAILED;                                                                               \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        NG_LAUNCH((latent_core_kernel<TT, HH>), n_rows, nwarp * 32, smem, stream, (const TT*)q, (const TT*)pages, table, \
+                  table_stride, positions, row_entry, gate, (TT*)out, nH, rp, page_size, num_pages, window, scale);    \
+    }
+    if (act_bf16) {
+        if (hpw == 1) LC_LAUNCH(__nv_bfloat16, 1) else if (hpw == 2) LC_LAUNCH(__nv_bfloat16, 2) else LC_LAUNCH(__nv_bfloat16, 4)
+    } else {
+        if (hpw == 1) LC_LAUNCH(float, 1) else if (hpw == 2) LC_LAUNCH(float, 2) else LC_LAUNCH(float, 4)
+    }
+    return ng_launch_status();
 }
 
 NG_EXPORT int ng_latent_prep(const void* x, const float* wq, const float* wkv, void* cq_out, void* pages,

@@ -377,9 +377,12 @@ def input_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: 
 # ----------------------------------------------------------------------------- retention
 def retention(x: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int, decay: torch.Tensor,
               state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor,
-              slots: torch.Tensor, n_entries: int, n_heads: int, key_dim: int, value_dim: int, eps: float) -> None:
+              slots: torch.Tensor, n_entries: int, n_heads: int, key_dim: int, value_dim: int, eps: float,
+              chunked: bool = False) -> None:
     """x[N, 2*nH*(dk+dv)] = q|k|v|g;  per head S = decay*S + k v^T, o = S^T q, out[N, nH*dv] = o/rms(o) * silu(g);
-    state[slots, nH, dk, dv] float32.  q, k rotated on their first ``rot_dims`` coordinates (pairs i, i+rot_dims/2)."""
+    state[slots, nH, dk, dv] float32.  q, k rotated on their first ``rot_dims`` coordinates (pairs i, i+rot_dims/2).
+    ``chunked``: the kernel for long portions, which regroups the sums chunk by chunk (``retention_chunked_takes``
+    tells whether it takes the head sizes); else the token-by-token kernel."""
     n = x.shape[0]
     if x.shape[1] != 2 * n_heads * (key_dim + value_dim) or out.shape != (n, n_heads * value_dim) \
             or out.dtype != x.dtype or state.shape[1:] != (n_heads, key_dim, value_dim) or decay.numel() != n_heads:
@@ -388,11 +391,16 @@ def retention(x: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int, 
         raise KernelError("retention: inv_freq must hold rot_dims/2 frequencies")
     _f32(inv_freq, "inv_freq"), _f32(decay, "decay"), _f32(state, "retention state")
     _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
-    f = _fn("retention", "ng_retention", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 4
+    f = _fn("retention", "ng_retention_chunked" if chunked else "ng_retention", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 4
             + [_c_float, _c_int, _c_void_p])
     _check(f(_ptr(x), _ptr(inv_freq), int(rot_dims), _ptr(decay), _ptr(state), _ptr(out), _ptr(cu_q),
              _ptr(ctx_before), _ptr(slots), n_entries, n_heads, key_dim, value_dim, float(eps),
              _act_flag(x, "retention input"), _stream()), "retention")
+
+
+def retention_chunked_takes(key_dim: int, value_dim: int) -> bool:
+    f = _fn("retention", "ng_retention_chunked_takes", [_c_int, _c_int])
+    return bool(f(int(key_dim), int(value_dim)))
 
 
 # ----------------------------------------------------------------------------- latent attention
@@ -415,6 +423,28 @@ def latent_prep(x: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, cq_out: to
     _check(f(_ptr(x), _ptr(wq), _ptr(wkv), _ptr(cq_out), _ptr(pages), _ptr(gate_out), _ptr(table), table.shape[1],
              _ptr(positions), _ptr(row_entry), n, rq, rkv, rp, n_heads, page_size, num_pages, float(eps),
              _ptr(status), _act_flag(x, "latent input"), _stream()), "latent_prep")
+
+
+def latent_core_takes(n_heads: int, rank: int) -> bool:
+    """Whether the latent attention core takes this many heads of this many (padded) latent columns."""
+    return n_heads <= 64 and rank <= 256 and (32 * (rank + 1) + n_heads * rank) * 4 <= 200 * 1024
+
+
+def latent_core(q: torch.Tensor, pages: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+                row_entry: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_heads: int,
+                window: Optional[int], scale: float) -> None:
+    """out[N, nH*r] = gate[N, nH] * softmax(q_h . c_j * scale over the visible j) c_j, every head reading the same
+    latent pages[P, 1, page, r] as keys and as values; float32 scores, weights and sums."""
+    n = q.shape[0]
+    num_pages, one, page_size, rp = pages.shape
+    if q.shape != (n, n_heads * rp) or out.shape != q.shape or one != 1 or q.dtype != pages.dtype or out.dtype != q.dtype \
+            or (gate is not None and gate.shape != (n, n_heads)):
+        raise KernelError("latent_core: shapes or dtypes do not fit")
+    _f32(gate, "gate"), _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
+    f = _fn("latent", "ng_latent_core", [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 6 + [_c_float, _c_int, _c_void_p])
+    _check(f(_ptr(q), _ptr(pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry), _ptr(gate), _ptr(out),
+             n, n_heads, rp, page_size, num_pages, int(window or 0), float(scale), _act_flag(q, "q"), _stream()),
+           "latent_core")
 
 
 def head_gate(y: torch.Tensor, gate: torch.Tensor, n_heads: int) -> None:
@@ -456,10 +486,11 @@ def moe_scale(act: torch.Tensor, weights: torch.Tensor, expert_ff: int) -> None:
 def token_side(h: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor,
                w_proj: torch.Tensor, w_norm: torch.Tensor, row_entry: torch.Tensor, eps: float,
                status: torch.Tensor) -> None:
-    """h[N,H] float32 += rmsnorm(W_proj (gelu_tanh(W_gate h) * table[tokens])) * w_norm; all float32."""
+    """h[N,H] float32 += rmsnorm(W_proj (gelu_tanh(W_gate h) * table[tokens])) * w_norm; all float32.
+    ``w_proj`` is given transposed, [dim, H]."""
     n, H = h.shape
     V, dim = table.shape
-    if w_gate.shape != (dim, H) or w_proj.shape != (H, dim) or w_norm.numel() != H:
+    if w_gate.shape != (dim, H) or w_proj.shape != (dim, H) or w_norm.numel() != H:
         raise KernelError("token_side: shapes do not fit")
     for t, what in ((h, "residual stream"), (table, "token table"), (w_gate, "gate"), (w_proj, "proj"), (w_norm, "norm")):
         _f32(t, what)

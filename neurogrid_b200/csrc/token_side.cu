@@ -1,62 +1,132 @@
-// Per-layer token input: x += rmsnorm(W_proj (gelu_tanh(W_gate x) * e[token])) * w, one block per row.
+// Per-layer token input: x += rmsnorm(W_proj (gelu_tanh(W_gate x) * e[token])) * w.
 //
 //   x: the float32 residual stream [n_rows, H], complete (every pending sum added);
-//   e: [vocab, dim] float32, the layer's columns of the token table;  W_gate [dim, H], W_proj [H, dim], w [H] float32.
-// Everything is float32: the row's dim gate values, then y = W_proj g (kept in shared memory), its mean
-// square, and the sum into the stream.  A row's result does not depend on the batch.
+//   e: [vocab, dim] float32, the layer's columns of the token table;
+//   W_gate [dim, H], W_proj^T [dim, H] (transposed when bound, so that both are read along H), w [H] float32.
+// Everything is float32.  A block takes R rows (8 for long steps, so that the two matrices are read once per
+// eight rows; 1 for short ones): the rows are staged in shared memory, a warp per gate value forms the
+// R dot products, then a thread per column forms y for the R rows, which replaces the staged rows; the
+// mean squares are reduced per row and the sum goes into the stream.  A row's arithmetic does not depend
+// on R or on the other rows: every dot product is walked in the same order.
 #include "ng_common.cuh"
 
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-__global__ void __launch_bounds__(256)
+#define TS_THREADS 512
+
+template <int R>
+__global__ void __launch_bounds__(TS_THREADS)
 token_side_kernel(float* __restrict__ h, const int* __restrict__ tokens, const float* __restrict__ table,
-                  const float* __restrict__ w_gate, const float* __restrict__ w_proj, const float* __restrict__ w_norm,
-                  int H, int dim, int vocab, float eps, const int* __restrict__ row_entry, int* __restrict__ status) {
+                  const float* __restrict__ w_gate, const float* __restrict__ w_proj_t, const float* __restrict__ w_norm,
+                  int n_rows, int H, int dim, int vocab, float eps, const int* __restrict__ row_entry,
+                  int* __restrict__ status) {
     extern __shared__ float sm[];
-    float* g = sm;              // [dim]
-    float* y = sm + dim;        // [H]
-    __shared__ float red[32];
+    float* buf = sm;                 // [R][H]: the rows, then y
+    float* g = sm + (size_t)R * H;   // [R][dim]
+    __shared__ float red[R][TS_THREADS / 32];
+    __shared__ float scale[R];
     ng_pdl_trigger();
     ng_pdl_wait();
-    const int row = blockIdx.x;
-    if (row_entry[row] < 0) return;
-    int tok = tokens[row];
-    if (tok < 0 || tok >= vocab) {
-        if (threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_TOKEN);
-        tok = 0;
+    const int r0 = blockIdx.x * R;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = TS_THREADS / 32;
+    bool live[R];
+    int tok[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        live[r] = r0 + r < n_rows && row_entry[r0 + r] >= 0;
+        tok[r] = live[r] ? tokens[r0 + r] : 0;
+        if (tok[r] < 0 || tok[r] >= vocab) {
+            if (tid == 0) atomicOr(status, NG_STATUS_BAD_TOKEN);
+            tok[r] = 0;
+        }
     }
-    float* hr = h + (size_t)row * H;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    for (int i = warp; i < dim; i += nwarp) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+        for (int j = tid; j < H; j += TS_THREADS) buf[(size_t)r * H + j] = live[r] ? h[(size_t)(r0 + r) * H + j] : 0.f;
+    __syncthreads();
+    for (int i = warp; i < dim; i += NW) {
         const float* w = w_gate + (size_t)i * H;
-        float acc = 0.f;
-        for (int j = lane; j < H; j += 32) acc = fmaf(hr[j], w[j], acc);
-        acc = ng_warp_sum(acc);
-        if (lane == 0) g[i] = gelu_tanh(acc) * table[(size_t)tok * dim + i];
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        for (int j = lane; j < H; j += 32) {
+            const float wv = w[j];
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = fmaf(buf[(size_t)r * H + j], wv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float a = ng_warp_sum(acc[r]);
+            if (lane == 0) g[r * dim + i] = gelu_tanh(a) * table[(size_t)tok[r] * dim + i];
+        }
     }
     __syncthreads();
-    float ss = 0.f;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        const float* w = w_proj + (size_t)j * dim;
-        float acc = 0.f;
-        for (int i = 0; i < dim; ++i) acc = fmaf(w[i], g[i], acc);
-        y[j] = acc;
-        ss += acc * acc;
+    float ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) ss[r] = 0.f;
+    for (int j = tid; j < H; j += TS_THREADS) {
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        for (int i = 0; i < dim; ++i) {
+            const float wv = w_proj_t[(size_t)i * H + j];
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = fmaf(wv, g[r * dim + i], acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            buf[(size_t)r * H + j] = acc[r];          // each thread re-reads only what it wrote itself
+            ss[r] += acc[r] * acc[r];
+        }
     }
-    ss = ng_block_sum(ss, red);
-    const float r = rsqrtf(ss / (float)H + eps);
-    for (int j = threadIdx.x; j < H; j += blockDim.x) hr[j] += y[j] * r * w_norm[j];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const float s = ng_warp_sum(ss[r]);
+        if (lane == 0) red[r][warp] = s;
+    }
+    __syncthreads();
+    if (tid < R) {
+        float s = 0.f;
+        for (int k = 0; k < NW; ++k) s += red[tid][k];
+        scale[tid] = rsqrtf(s / (float)H + eps);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (!live[r]) continue;
+        float* hr = h + (size_t)(r0 + r) * H;
+        for (int j = tid; j < H; j += TS_THREADS) hr[j] += buf[(size_t)r * H + j] * scale[r] * w_norm[j];
+    }
 }
 
-NG_EXPORT int ng_token_side(float* h, const int* tokens, const float* table, const float* w_gate, const float* w_proj,
+template <int R>
+static int token_side_launch(float* h, const int* tokens, const float* table, const float* w_gate, const float* w_proj_t,
+                             const float* w_norm, const int* row_entry, int n_rows, int H, int dim, int vocab, float eps,
+                             int* status, cudaStream_t stream) {
+    const size_t smem = (size_t)R * ((size_t)H + dim) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(token_side_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        configured = true;
+    }
+    NG_LAUNCH((token_side_kernel<R>), (n_rows + R - 1) / R, TS_THREADS, smem, stream, h, tokens, table, w_gate, w_proj_t,
+              w_norm, n_rows, H, dim, vocab, eps, row_entry, status);
+    return ng_launch_status();
+}
+
+NG_EXPORT int ng_token_side(float* h, const int* tokens, const float* table, const float* w_gate, const float* w_proj_t,
                             const float* w_norm, const int* row_entry, int n_rows, int H, int dim, int vocab, float eps,
                             int* status, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    const size_t smem = ((size_t)dim + H) * sizeof(float);
-    if (H <= 0 || dim <= 0 || vocab <= 0 || smem > 48 * 1024) return NG_BAD_SIZE;
-    NG_LAUNCH((token_side_kernel), n_rows, 256, smem, stream, h, tokens, table, w_gate, w_proj, w_norm, H, dim, vocab, eps,
-              row_entry, status);
-    return ng_launch_status();
+    if (H <= 0 || dim <= 0 || vocab <= 0) return NG_BAD_SIZE;
+    const size_t per_row = ((size_t)H + dim) * sizeof(float), cap = 160 * 1024;
+    if (per_row > cap) return NG_BAD_SIZE;
+#define TS_GO(RR) return token_side_launch<RR>(h, tokens, table, w_gate, w_proj_t, w_norm, row_entry, n_rows, H, dim, vocab, eps, status, stream)
+    if (n_rows >= 512 && 8 * per_row <= cap) TS_GO(8);
+    if (n_rows >= 128 && 4 * per_row <= cap) TS_GO(4);
+    TS_GO(1);
 }

@@ -58,7 +58,7 @@ class TokenSide:
         n = self.spec.names
         f32 = dict(device=self.device, dtype=torch.float32)
         self.w_gate = t[n["gate"]].to(**f32).contiguous()
-        self.w_proj = t[n["proj"]].to(**f32).contiguous()
+        self.w_proj = t[n["proj"]].to(**f32).t().contiguous()          # [dim, hidden]: the kernel reads both matrices along hidden
         self.w_norm = t[n["norm"]].to(**f32).contiguous()
 
     def bind_shared(self, weights):

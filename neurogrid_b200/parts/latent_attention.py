@@ -20,8 +20,9 @@ class LatentAttention:
         q_h . k_h = (W_uk,h^T W_uq,h c_q) . c        -> one matrix [heads * rank, q_rank] makes the queries
         W_o,h (g_h * W_uv,h sum_j p_j c_j)           -> one matrix [hidden, heads * rank] ends the mixer
     so the attention core is a multi-query attention in which every head reads the latent pages both as
-    keys and as values.  Scores, softmax weights and their sum with the values are float32 (the
-    order-fixed kernel, one warp per row and head), as are the two norms and the gate."""
+    keys and as values: a block per row stages each tile of latents once for all heads.  Scores, softmax
+    weights and their sum with the values are float32, keys are walked in ascending order, and the two
+    norms and the gate are float32 too."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
 
@@ -80,7 +81,11 @@ class LatentAttention:
         q = ctx.ws.buf("lat_q", n, H * rp, self.dtype)
         ops.linear(cq, self.w_q, None, q)
         o = ctx.ws.buf("lat_o", n, H * rp, self.dtype)
-        ops.attention_generic(q, cache.k_pages, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, o,
-                              H, s.window, s.softmax_scale)
-        ops.head_gate(o, gate, H)
+        if ops.latent_core_takes(H, rp):
+            ops.latent_core(q, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, gate, o, H, s.window,
+                            s.softmax_scale)
+        else:                                   # very many heads or a very wide latent: the plain kernel, then the gate
+            ops.attention_generic(q, cache.k_pages, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, o,
+                                  H, s.window, s.softmax_scale)
+            ops.head_gate(o, gate, H)
         return ops.linear_to_residual(o, self.w_out, None, ctx.ws, "mixer_out", residual=ctx.residual)

@@ -22,6 +22,7 @@ class Retention:
     State per request: S [heads, key_dim, value_dim], float32, zero at admission."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    CHUNKED_MIN_ROWS = 16  # a step whose longest portion has this many tokens runs the chunk-by-chunk kernel
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
@@ -59,6 +60,10 @@ class Retention:
             raise NotImplementedError("the retention kernel rotates pairs (i, i + dims/2) of unscaled positions")
         rot = 0 if pa.inv_freq is None else (s.key_dim if pa.rotary_dims is None else pa.rotary_dims)
         o = ctx.ws.buf("ret_out", n, s.n_heads * s.value_dim, self.dtype)
+        # float32 keeps the token-by-token kernel for every step: there a token's arithmetic is the same however
+        # its request is cut.  bfloat16 steps with a long portion regroup the sums chunk by chunk.
+        chunked = (self.dtype == torch.bfloat16 and ctx.max_q >= self.CHUNKED_MIN_ROWS
+                   and ops.retention_chunked_takes(s.key_dim, s.value_dim))
         ops.retention(p, pa.inv_freq if rot else None, rot, self.decay, cache.state, o, ctx.cu_q, ctx.ctx_before,
-                      ctx.slots, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim, s.eps)
+                      ctx.slots, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim, s.eps, chunked=chunked)
         return ops.linear_to_residual(o, self.w_o, None, ctx.ws, "mixer_out", residual=ctx.residual)

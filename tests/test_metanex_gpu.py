@@ -143,6 +143,40 @@ def test_retention_whole_cut_and_decode(dtype, heads, dk, dv, rot):
         assert rel_err(cut, whole) < 1e-6
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dk,dv,rot", [(3, 32, 20, 16), (2, 64, 64, 64), (1, 16, 136, 0), (2, 128, 128, 32)])
+def test_retention_chunk_kernel(dtype, heads, dk, dv, rot):
+    """The kernel for long portions, called directly in both dtypes: whole, cut inside chunks and at their edges,
+    beside a second request, and continued by the token-by-token kernel on the same state."""
+    from neurogrid_b200.csrc import ops
+    H, T = 96, 150
+    decay = [0.999, 0.9, 1.0][:heads]
+    pos = RopeSpec(dk, 300.0, "half", rotary_dims=rot) if rot else NoPositionSpec()
+    part, w, m = _retention(RetentionSpec(H, heads, dk, dv, tuple(decay), pos, 1e-5), dtype)
+    assert ops.retention_chunked_takes(dk, dv)
+    x = _x(T, H, dtype)
+    want = plain.retention(x.double().cpu(), w, "mix.", m, 1e-5, plain.bf16 if dtype == torch.bfloat16 else plain.same)
+    wo = w["mix.o"].T
+    p = (x @ part.w_in.T).contiguous()
+    state = torch.randn(4, heads, dk, dv, device=DEV)
+
+    def run(cuts, slot, chunked):
+        outs = []
+        for (at, n), ch in zip(cuts, chunked):
+            ctx = make_ctx([n], [at], [slot], dtype=dtype)
+            o = torch.empty(n, heads * dv, dtype=dtype, device=DEV)
+            ops.retention(p[at:at + n].contiguous(), part.position.inv_freq if rot else None, rot, part.decay, state, o,
+                          ctx.cu_q, ctx.ctx_before, ctx.slots, 1, heads, dk, dv, 1e-5, chunked=ch)
+            outs.append(o)
+        return torch.cat(outs).double().cpu() @ wo
+
+    assert rel_err(run([(0, T)], 0, [True]), want) < TOL[dtype]
+    cuts = _cuts(T, [32, 5, 64, 1, 31, 2])
+    assert rel_err(run(cuts, 1, [True] * len(cuts)), want) < TOL[dtype]
+    assert rel_err(run(cuts, 2, [i % 2 == 0 for i in range(len(cuts))]), want) < TOL[dtype]
+    assert torch.allclose(state[0], state[1], rtol=1e-3, atol=1e-4) and torch.allclose(state[0], state[2], rtol=1e-3, atol=1e-4)
+
+
 def test_retention_reads_a_far_key():
     """One key, 700 tokens back, is made to stand out for the last query (same direction, large): a head that decays
     slowly must still answer with its value, a head that decays fast must not."""
@@ -155,6 +189,9 @@ def test_retention_reads_a_far_key():
     state = torch.zeros(2, 2, dk, dv, device=DEV)
     got = _run_retention(part, x, [(0, 500), (500, 259), (759, 1)], torch.float32, 0, state)
     assert rel_err(got, want) < 1e-4
+    part16, _, _ = _retention(spec, torch.bfloat16, seed=3)          # the chunk-by-chunk kernel of the bfloat16 path
+    got16 = _run_retention(part16, x.to(torch.bfloat16), [(0, 500), (500, 259), (759, 1)], torch.bfloat16, 1, state)
+    assert rel_err(got16[-1], want[-1]) < 3e-2
     x2 = x.clone()
     x2[40] = x[41]                                                # without the far token the last answer differs much
     other = plain.retention(x2.double().cpu(), w, "mix.", m, 1e-5)
@@ -193,7 +230,7 @@ def _run_latent(part, x, cuts, dtype, ps=8, pages=40, seed=0):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dk,dv,rq,rkv,window", [(3, 16, 24, 40, 20, 21), (2, 32, 32, 24, 64, None),
                                                        (5, 8, 4, 16, 100, 8), (1, 64, 16, 8, 16, 1),
-                                                       (18, 8, 8, 16, 24, 30)])
+                                                       (18, 8, 8, 16, 24, 30), (33, 4, 4, 8, 250, 12), (70, 4, 4, 8, 16, 9)])
 def test_latent_attention_whole_cut_and_decode(dtype, heads, dk, dv, rq, rkv, window):
     H, T = 80, 70
     spec = LatentAttentionSpec(H, heads, dk, dv, rq, rkv, 0.4, 2e-5, window)
