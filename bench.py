@@ -727,9 +727,12 @@ def metanex_kernel_times(eng, l2, pk):
         ro = torch.empty(rows, s.n_heads * s.value_dim, dtype=torch.bfloat16, device=dev)
         state = torch.zeros(8, s.n_heads, s.key_dim, s.value_dim, device=dev)
         chunked = q >= ret.CHUNKED_MIN_ROWS
+        scr = torch.empty(rows, s.n_heads * s.value_dim, device=dev) if chunked else None
+        sts = torch.empty(ops.retention_chunked_scratch(rows, entries, s.n_heads, s.key_dim, s.value_dim), device=dev) if chunked else None
         us = timed(lambda: ops.retention(x, ret.position.inv_freq, s.position.rotary_dims, ret.decay, state, ro, cu, cb, sl,
-                                         entries, s.n_heads, s.key_dim, s.value_dim, s.eps, chunked=chunked))
-        nbytes = x.numel() * 2 + ro.numel() * 2 + 2 * entries * state[0].numel() * 4
+                                         entries, s.n_heads, s.key_dim, s.value_dim, s.eps, scratch=scr, state_scratch=sts,
+                                         max_q=q))
+        nbytes = x.numel() * 2 + ro.numel() * 2 + 2 * entries * state[0].numel() * 4 + (3 * sts.numel() * 4 + 2 * scr.numel() * 4 if chunked else 0)
         mem(f"{tag}_retention", us, nbytes)
         if chunked:
             C = 32

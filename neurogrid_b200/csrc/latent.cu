@@ -71,6 +71,7 @@ __global__ void head_gate_kernel(T* __restrict__ y, const float* __restrict__ ga
 // The head's gate multiplies the result before it is stored.
 #define LC_TILE 32
 #define LC_MAX_J 8       // columns per lane: rank <= 256
+#define LC_VPT 8         // 16-byte vectors a thread fetches per tile: 32 keys x 256 float32 columns / 256 threads
 
 template <typename T, int HPW>
 __global__ void __launch_bounds__(512)
@@ -103,17 +104,41 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
 #pragma unroll
         for (int j = 0; j < LC_MAX_J; ++j) acc[u][j] = 0.f;
     }
+    // Tiles are fetched 16 bytes a thread and load, a tile ahead: the loads of tile t+1 are in flight while the
+    // warps work on tile t.  LC_VPT vectors a thread cover 32 keys of up to 256 columns at 256 threads and more.
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int vec_per_key = rp / VEC;                       // rp is a multiple of 16
+    uint4 pre[LC_VPT];
+    auto fetch = [&](int k0) {
+        const int n = min(LC_TILE, pos + 1 - k0);
+#pragma unroll
+        for (int v = 0; v < LC_VPT; ++v) {
+            const int idx = tid + v * blockDim.x;
+            pre[v] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < n * vec_per_key) {
+                const int kp = k0 + idx / vec_per_key;
+                const int page = trow[kp / page_size];
+                if (page >= 0 && page < num_pages)
+                    pre[v] = *reinterpret_cast<const uint4*>(pages + ((size_t)page * page_size + (kp % page_size)) * rp
+                                                             + (size_t)(idx % vec_per_key) * VEC);
+            }
+        }
+    };
+    fetch(lo);
     for (int k0 = lo; k0 <= pos; k0 += LC_TILE) {
         const int n = min(LC_TILE, pos + 1 - k0);
         __syncthreads();
-        for (int idx = tid; idx < n * rp; idx += blockDim.x) {
-            const int k = idx / rp, d = idx % rp;
-            const int kp = k0 + k;
-            const int page = trow[kp / page_size];
-            float v = 0.f;
-            if (page >= 0 && page < num_pages) v = ng_ld(pages + ((size_t)page * page_size + (kp % page_size)) * rp + d);
-            Ts[k * ldt + d] = v;
+#pragma unroll
+        for (int v = 0; v < LC_VPT; ++v) {
+            const int idx = tid + v * blockDim.x;
+            if (idx < n * vec_per_key) {
+                const T* e = reinterpret_cast<const T*>(&pre[v]);
+                float* dst = Ts + (idx / vec_per_key) * ldt + (idx % vec_per_key) * VEC;
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) dst[c] = ng_ld(e + c);
+            }
         }
+        if (k0 + LC_TILE <= pos) fetch(k0 + LC_TILE);
         __syncthreads();
 #pragma unroll
         for (int u = 0; u < HPW; ++u) {
@@ -164,7 +189,7 @@ NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table,
                              int num_pages, int window, float scale, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (nH <= 0 || rp <= 0 || rp > 32 * LC_MAX_J || page_size <= 0 || nH > 64) return NG_BAD_SIZE;
-    const int nwarp = nH <= 16 ? nH : 16;
+    const int nwarp = nH <= 8 ? 8 : nH <= 16 ? nH : 16;           // at least 256 threads: all of them fetch the tiles
     const int hpw = (nH + nwarp - 1) / nwarp;
     const size_t smem = ((size_t)LC_TILE * (rp + 1) + (size_t)nH * rp) * sizeof(float);
     if (smem > 200 * 1024) return NG_BAD_SIZE;

@@ -11,6 +11,13 @@
 
 #define MOE_MAX_TOP 32
 
+__device__ __forceinline__ float4 moe_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 moe_ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_router_kernel(const T* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
@@ -24,7 +31,15 @@ moe_router_kernel(const T* __restrict__ x, const float* __restrict__ wr, const f
     for (int e = warp; e < E; e += nwarp) {
         const float* w = wr + (size_t)e * H;
         float acc = 0.f;
-        for (int i = lane; i < H; i += 32) acc = fmaf(ng_ld(xr + i), w[i], acc);
+        if (H % 4 == 0) {                           // four columns a lane and load; the order depends on H alone
+#pragma unroll 4
+            for (int i = lane * 4; i < H; i += 128) {
+                const float4 xv = moe_ld4(xr + i), wv = moe_ld4(w + i);
+                acc = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc))));
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) acc = fmaf(ng_ld(xr + i), w[i], acc);
+        }
         acc = ng_warp_sum(acc);
         if (lane == 0) z[e] = acc + (br ? br[e] : 0.f);
     }

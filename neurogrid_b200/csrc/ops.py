@@ -378,24 +378,44 @@ def input_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: 
 def retention(x: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dims: int, decay: torch.Tensor,
               state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor,
               slots: torch.Tensor, n_entries: int, n_heads: int, key_dim: int, value_dim: int, eps: float,
-              chunked: bool = False) -> None:
+              scratch: Optional[torch.Tensor] = None, state_scratch: Optional[torch.Tensor] = None,
+              max_q: int = 0) -> None:
     """x[N, 2*nH*(dk+dv)] = q|k|v|g;  per head S = decay*S + k v^T, o = S^T q, out[N, nH*dv] = o/rms(o) * silu(g);
     state[slots, nH, dk, dv] float32.  q, k rotated on their first ``rot_dims`` coordinates (pairs i, i+rot_dims/2).
-    ``chunked``: the kernel for long portions, which regroups the sums chunk by chunk (``retention_chunked_takes``
-    tells whether it takes the head sizes); else the token-by-token kernel."""
+    With ``scratch`` (float32 [N, nH*dv]), ``state_scratch`` (``retention_chunked_scratch`` float32 values) and
+    ``max_q`` (the longest portion) the kernels for long portions run, which regroup the sums chunk by chunk and run
+    the chunks side by side (``retention_chunked_takes`` tells whether they take the head sizes); else the
+    token-by-token kernel."""
     n = x.shape[0]
     if x.shape[1] != 2 * n_heads * (key_dim + value_dim) or out.shape != (n, n_heads * value_dim) \
             or out.dtype != x.dtype or state.shape[1:] != (n_heads, key_dim, value_dim) or decay.numel() != n_heads:
         raise KernelError("retention: shapes do not fit")
     if rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2):
         raise KernelError("retention: inv_freq must hold rot_dims/2 frequencies")
-    _f32(inv_freq, "inv_freq"), _f32(decay, "decay"), _f32(state, "retention state")
+    _f32(inv_freq, "inv_freq"), _f32(decay, "decay"), _f32(state, "retention state"), _f32(scratch, "retention scratch")
     _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
-    f = _fn("retention", "ng_retention_chunked" if chunked else "ng_retention", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 4
+    act = _act_flag(x, "retention input")
+    if scratch is not None:
+        need = retention_chunked_scratch(n, n_entries, n_heads, key_dim, value_dim)
+        if scratch.shape != out.shape or state_scratch is None or state_scratch.dtype != torch.float32 \
+                or state_scratch.numel() < need or max_q <= 0:
+            raise KernelError(f"retention: the chunked kernels need a scratch of the output's shape, {need} float32 "
+                              "values for the chunks' states and the longest portion's length")
+        f = _fn("retention", "ng_retention_chunked", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 8 + [_c_int] * 6
+                + [_c_float, _c_int, _c_void_p])
+        _check(f(_ptr(x), _ptr(inv_freq), int(rot_dims), _ptr(decay), _ptr(state), _ptr(out), _ptr(scratch),
+                 _ptr(state_scratch), _ptr(cu_q), _ptr(ctx_before), _ptr(slots), n_entries, n, int(max_q), n_heads,
+                 key_dim, value_dim, float(eps), act, _stream()), "retention (chunked)")
+        return
+    f = _fn("retention", "ng_retention", [_c_void_p, _c_void_p, _c_int] + [_c_void_p] * 6 + [_c_int] * 4
             + [_c_float, _c_int, _c_void_p])
     _check(f(_ptr(x), _ptr(inv_freq), int(rot_dims), _ptr(decay), _ptr(state), _ptr(out), _ptr(cu_q),
-             _ptr(ctx_before), _ptr(slots), n_entries, n_heads, key_dim, value_dim, float(eps),
-             _act_flag(x, "retention input"), _stream()), "retention")
+             _ptr(ctx_before), _ptr(slots), n_entries, n_heads, key_dim, value_dim, float(eps), act, _stream()), "retention")
+
+
+def retention_chunked_scratch(n_rows: int, n_entries: int, n_heads: int, key_dim: int, value_dim: int) -> int:
+    """float32 values the chunked retention kernels need for the chunks' states."""
+    return (n_rows // 32 + n_entries + 1) * n_heads * key_dim * value_dim
 
 
 def retention_chunked_takes(key_dim: int, value_dim: int) -> bool:

@@ -47,15 +47,28 @@ token_side_kernel(float* __restrict__ h, const int* __restrict__ tokens, const f
     for (int r = 0; r < R; ++r)
         for (int j = tid; j < H; j += TS_THREADS) buf[(size_t)r * H + j] = live[r] ? h[(size_t)(r0 + r) * H + j] : 0.f;
     __syncthreads();
+    const bool vec = (H % 4) == 0;                       // rows of the matrices start on 16-byte boundaries
     for (int i = warp; i < dim; i += NW) {
         const float* w = w_gate + (size_t)i * H;
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = 0.f;
-        for (int j = lane; j < H; j += 32) {
-            const float wv = w[j];
+        if (vec) {
+#pragma unroll 4
+            for (int j = lane * 4; j < H; j += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + j);
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] = fmaf(buf[(size_t)r * H + j], wv, acc[r]);
+                for (int r = 0; r < R; ++r) {
+                    const float4 xv = *reinterpret_cast<const float4*>(buf + (size_t)r * H + j);
+                    acc[r] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[r]))));
+                }
+            }
+        } else {
+            for (int j = lane; j < H; j += 32) {
+                const float wv = w[j];
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r] = fmaf(buf[(size_t)r * H + j], wv, acc[r]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -67,21 +80,47 @@ token_side_kernel(float* __restrict__ h, const int* __restrict__ tokens, const f
     float ss[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) ss[r] = 0.f;
-    for (int j = tid; j < H; j += TS_THREADS) {
-        float acc[R];
+    if (vec) {
+        for (int j = tid * 4; j < H; j += 4 * TS_THREADS) {          // four columns a thread
+            float4 acc[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) acc[r] = 0.f;
-        for (int i = 0; i < dim; ++i) {
-            const float wv = w_proj_t[(size_t)i * H + j];
+            for (int r = 0; r < R; ++r) acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int i = 0; i < dim; ++i) {
+                const float4 wv = *reinterpret_cast<const float4*>(w_proj_t + (size_t)i * H + j);
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] = fmaf(wv, g[r * dim + i], acc[r]);
+                for (int r = 0; r < R; ++r) {
+                    const float gv = g[r * dim + i];
+                    acc[r].x = fmaf(wv.x, gv, acc[r].x);
+                    acc[r].y = fmaf(wv.y, gv, acc[r].y);
+                    acc[r].z = fmaf(wv.z, gv, acc[r].z);
+                    acc[r].w = fmaf(wv.w, gv, acc[r].w);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                *reinterpret_cast<float4*>(buf + (size_t)r * H + j) = acc[r];
+                ss[r] += acc[r].x * acc[r].x + acc[r].y * acc[r].y + acc[r].z * acc[r].z + acc[r].w * acc[r].w;
+            }
         }
+    } else {
+        for (int j = tid; j < H; j += TS_THREADS) {
+            float acc[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            buf[(size_t)r * H + j] = acc[r];          // each thread re-reads only what it wrote itself
-            ss[r] += acc[r] * acc[r];
+            for (int r = 0; r < R; ++r) acc[r] = 0.f;
+            for (int i = 0; i < dim; ++i) {
+                const float wv = w_proj_t[(size_t)i * H + j];
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r] = fmaf(wv, g[r * dim + i], acc[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                buf[(size_t)r * H + j] = acc[r];
+                ss[r] += acc[r] * acc[r];
+            }
         }
     }
+    __syncthreads();                                     // the sum below reads columns other threads wrote
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const float s = ng_warp_sum(ss[r]);

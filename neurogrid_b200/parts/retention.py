@@ -50,6 +50,13 @@ class Retention:
     def kernels(self):
         return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("retention", None)]
 
+    def scratch_bytes_per_row(self):
+        """Workspace per row besides the products' outputs: the heads' outputs before their norm and the chunks' states."""
+        s = self.spec
+        if self.dtype != torch.bfloat16:
+            return 0
+        return 4 * s.n_heads * s.value_dim + 4 * s.n_heads * s.key_dim * s.value_dim // 32
+
     def forward(self, x, ctx, cache):
         s = self.spec
         n = x.shape[0]
@@ -64,6 +71,14 @@ class Retention:
         # its request is cut.  bfloat16 steps with a long portion regroup the sums chunk by chunk.
         chunked = (self.dtype == torch.bfloat16 and ctx.max_q >= self.CHUNKED_MIN_ROWS
                    and ops.retention_chunked_takes(s.key_dim, s.value_dim))
+        scratch = states = None
+        if chunked:
+            scratch = ctx.ws.buf("ret_scratch", n, s.n_heads * s.value_dim, torch.float32)
+            need = ops.retention_chunked_scratch(n, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim)
+            bound = ops.retention_chunked_scratch(ctx.ws.max_rows, ctx.ws.max_rows // self.CHUNKED_MIN_ROWS + 64,
+                                                  s.n_heads, s.key_dim, s.value_dim)
+            states = ctx.ws.flat("ret_states", need, torch.float32, reserve=max(need, bound))
         ops.retention(p, pa.inv_freq if rot else None, rot, self.decay, cache.state, o, ctx.cu_q, ctx.ctx_before,
-                      ctx.slots, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim, s.eps, chunked=chunked)
+                      ctx.slots, ctx.n_entries, s.n_heads, s.key_dim, s.value_dim, s.eps, scratch=scratch,
+                      state_scratch=states, max_q=ctx.max_q)
         return ops.linear_to_residual(o, self.w_o, None, ctx.ws, "mixer_out", residual=ctx.residual)

@@ -144,7 +144,8 @@ def test_retention_whole_cut_and_decode(dtype, heads, dk, dv, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dk,dv,rot", [(3, 32, 20, 16), (2, 64, 64, 64), (1, 16, 136, 0), (2, 128, 128, 32)])
+@pytest.mark.parametrize("heads,dk,dv,rot", [(3, 32, 20, 16), (2, 64, 64, 64), (1, 16, 136, 0), (2, 128, 128, 32),
+                                             (2, 22, 96, 10)])
 def test_retention_chunk_kernel(dtype, heads, dk, dv, rot):
     """The kernel for long portions, called directly in both dtypes: whole, cut inside chunks and at their edges,
     beside a second request, and continued by the token-by-token kernel on the same state."""
@@ -165,8 +166,11 @@ def test_retention_chunk_kernel(dtype, heads, dk, dv, rot):
         for (at, n), ch in zip(cuts, chunked):
             ctx = make_ctx([n], [at], [slot], dtype=dtype)
             o = torch.empty(n, heads * dv, dtype=dtype, device=DEV)
+            scratch = torch.empty(n, heads * dv, device=DEV) if ch else None
+            states = torch.empty(ops.retention_chunked_scratch(n, 1, heads, dk, dv), device=DEV) if ch else None
             ops.retention(p[at:at + n].contiguous(), part.position.inv_freq if rot else None, rot, part.decay, state, o,
-                          ctx.cu_q, ctx.ctx_before, ctx.slots, 1, heads, dk, dv, 1e-5, chunked=ch)
+                          ctx.cu_q, ctx.ctx_before, ctx.slots, 1, heads, dk, dv, 1e-5, scratch=scratch,
+                          state_scratch=states, max_q=n)
             outs.append(o)
         return torch.cat(outs).double().cpu() @ wo
 
