@@ -73,7 +73,7 @@ __global__ void head_gate_kernel(T* __restrict__ y, const float* __restrict__ ga
 #define LC_MAX_J 8       // columns per lane: rank <= 256
 #define LC_VPT 8         // 16-byte vectors a thread fetches per tile: 32 keys x 256 float32 columns / 256 threads
 
-template <typename T, int HPW>
+template <typename T, int HPW, int NJ>
 __global__ void __launch_bounds__(512)
 latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const int* __restrict__ table, int table_stride,
                    const int* __restrict__ positions, const int* __restrict__ row_entry, const float* __restrict__ gate,
@@ -96,13 +96,13 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* trow = table + (size_t)entry * table_stride;
     for (int i = tid; i < nH * rp; i += blockDim.x) qs[i] = ng_ld(q + (size_t)row * nH * rp + i) * scale;
-    float m[HPW], l[HPW], acc[HPW][LC_MAX_J];
+    float m[HPW], l[HPW], acc[HPW][NJ];
 #pragma unroll
     for (int u = 0; u < HPW; ++u) {
         m[u] = -INFINITY;
         l[u] = 0.f;
 #pragma unroll
-        for (int j = 0; j < LC_MAX_J; ++j) acc[u][j] = 0.f;
+        for (int j = 0; j < NJ; ++j) acc[u][j] = 0.f;
     }
     // Tiles are fetched 16 bytes a thread and load, a tile ahead: the loads of tile t+1 are in flight while the
     // warps work on tile t.  LC_VPT vectors a thread cover 32 keys of up to 256 columns at 256 threads and more.
@@ -145,12 +145,19 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
             const int head = warp + u * nwarp;
             if (head >= nH) break;
             const float* qh = qs + (size_t)head * rp;
-            float s = 0.f;
-            if (lane < n) {
+            float s = -INFINITY;
+            if (lane < n) {                     // four partial sums: the chain of one would wait on every load
                 const float* tk = Ts + lane * ldt;
-                for (int d = 0; d < rp; ++d) s = fmaf(qh[d], tk[d], s);
-            } else {
-                s = -INFINITY;
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 4
+                for (int d = 0; d < rp; d += 4) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qh + d);
+                    s0 = fmaf(qv.x, tk[d], s0);
+                    s1 = fmaf(qv.y, tk[d + 1], s1);
+                    s2 = fmaf(qv.z, tk[d + 2], s2);
+                    s3 = fmaf(qv.w, tk[d + 3], s3);
+                }
+                s = (s0 + s1) + (s2 + s3);
             }
             const float m_new = fmaxf(m[u], ng_warp_max(s));
             const float corr = expf(m[u] - m_new);
@@ -158,12 +165,13 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
             l[u] = l[u] * corr + ng_warp_sum(p);
             m[u] = m_new;
 #pragma unroll
-            for (int j = 0; j < LC_MAX_J; ++j) acc[u][j] *= corr;
+            for (int j = 0; j < NJ; ++j) acc[u][j] *= corr;
+#pragma unroll 4
             for (int k = 0; k < n; ++k) {
                 const float pk = __shfl_sync(0xffffffffu, p, k);
                 const float* tk = Ts + k * ldt;
 #pragma unroll
-                for (int j = 0; j < LC_MAX_J; ++j) {
+                for (int j = 0; j < NJ; ++j) {
                     const int d = lane + 32 * j;
                     if (d < rp) acc[u][j] = fmaf(pk, tk[d], acc[u][j]);
                 }
@@ -176,7 +184,7 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
         if (head >= nH) break;
         const float f = (l[u] > 0.f ? 1.f / l[u] : 0.f) * (gate ? gate[(size_t)row * nH + head] : 1.f);
 #pragma unroll
-        for (int j = 0; j < LC_MAX_J; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int d = lane + 32 * j;
             if (d < rp) ng_st(orow + (size_t)head * rp + d, acc[u][j] * f);
         }
@@ -193,22 +201,29 @@ NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table,
     const int hpw = (nH + nwarp - 1) / nwarp;
     const size_t smem = ((size_t)LC_TILE * (rp + 1) + (size_t)nH * rp) * sizeof(float);
     if (smem > 200 * 1024) return NG_BAD_SIZE;
-#define LC_LAUNCH(TT, HH)                                                                                              \
+#define LC_LAUNCH(TT, HH, JJ)                                                                                          \
     {                                                                                                                  \
         static bool configured = false;                                                                                \
         if (!configured) {                                                                                             \
-            if (cudaFuncSetAttribute(latent_core_kernel<TT, HH>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+            if (cudaFuncSetAttribute(latent_core_kernel<TT, HH, JJ>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
                                      200 * 1024) != cudaSuccess)                                                       \
                 return NG_LAUNCH_FAILED;                                                                               \
             configured = true;                                                                                         \
         }                                                                                                              \
-        NG_LAUNCH((latent_core_kernel<TT, HH>), n_rows, nwarp * 32, smem, stream, (const TT*)q, (const TT*)pages, table, \
-                  table_stride, positions, row_entry, gate, (TT*)out, nH, rp, page_size, num_pages, window, scale);    \
+        NG_LAUNCH((latent_core_kernel<TT, HH, JJ>), n_rows, nwarp * 32, smem, stream, (const TT*)q, (const TT*)pages,  \
+                  table, table_stride, positions, row_entry, gate, (TT*)out, nH, rp, page_size, num_pages, window,     \
+                  scale);                                                                                              \
+    }
+    // columns a lane keeps of a head's sum: the smallest of 1, 2, 4, 8 that covers the latent
+#define LC_BY_J(TT, HH)                                                                                                \
+    {                                                                                                                  \
+        if (rp <= 32) LC_LAUNCH(TT, HH, 1) else if (rp <= 64) LC_LAUNCH(TT, HH, 2) else if (rp <= 128) LC_LAUNCH(TT, HH, 4) \
+        else LC_LAUNCH(TT, HH, 8)                                                                                      \
     }
     if (act_bf16) {
-        if (hpw == 1) LC_LAUNCH(__nv_bfloat16, 1) else if (hpw == 2) LC_LAUNCH(__nv_bfloat16, 2) else LC_LAUNCH(__nv_bfloat16, 4)
+        if (hpw == 1) LC_BY_J(__nv_bfloat16, 1) else if (hpw == 2) LC_BY_J(__nv_bfloat16, 2) else LC_BY_J(__nv_bfloat16, 4)
     } else {
-        if (hpw == 1) LC_LAUNCH(float, 1) else if (hpw == 2) LC_LAUNCH(float, 2) else LC_LAUNCH(float, 4)
+        if (hpw == 1) LC_BY_J(float, 1) else if (hpw == 2) LC_BY_J(float, 2) else LC_BY_J(float, 4)
     }
     return ng_launch_status();
 }

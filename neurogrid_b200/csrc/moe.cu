@@ -19,7 +19,7 @@ __device__ __forceinline__ float4 moe_ld4(const __nv_bfloat16* p) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 moe_router_kernel(const T* __restrict__ x, const float* __restrict__ wr, const float* __restrict__ br,
                   float* __restrict__ weights, int H, int E, int top_k) {
     extern __shared__ float z[];               // [E]
@@ -90,11 +90,13 @@ NG_EXPORT int ng_moe_router(const void* x, const float* wr, const float* br, flo
     if (n_rows <= 0) return NG_OK;
     if (H <= 0 || E <= 0 || top_k < 1 || top_k > E || top_k > MOE_MAX_TOP || E > 8192) return NG_BAD_SIZE;
     const size_t smem = (size_t)E * sizeof(float);
+    // a warp per expert where rows are few (each dot product is a chain of loads), four warps a row otherwise
+    const int threads = n_rows <= 64 ? 32 * (E < 4 ? 4 : E > 16 ? 16 : E) : 128;
     if (act_bf16)
-        NG_LAUNCH((moe_router_kernel<__nv_bfloat16>), n_rows, 128, smem, stream, (const __nv_bfloat16*)x, wr, br, weights,
+        NG_LAUNCH((moe_router_kernel<__nv_bfloat16>), n_rows, threads, smem, stream, (const __nv_bfloat16*)x, wr, br, weights,
                   H, E, top_k);
     else
-        NG_LAUNCH((moe_router_kernel<float>), n_rows, 128, smem, stream, (const float*)x, wr, br, weights, H, E, top_k);
+        NG_LAUNCH((moe_router_kernel<float>), n_rows, threads, smem, stream, (const float*)x, wr, br, weights, H, E, top_k);
     return ng_launch_status();
 }
 

@@ -233,16 +233,25 @@ __global__ void retention_scan_kernel(float* __restrict__ u_scratch, float* __re
     float* S = state + ((size_t)slots[e] * nH + head) * dk * dv + i;
     float s = ctx_before[e] > 0 ? *S : 0.f;
     const int nc = (qlen + RC - 1) / RC;
-    for (int c = 0; c < nc; ++c) {
-        float* U = u_scratch + (((size_t)(q0 / RC + e + c)) * nH + head) * dk * dv + i;
-        const float u = *U;
-        *U = s;
-        float f = full;
-        if (c == nc - 1 && qlen % RC) {
-            f = 1.f;
-            for (int k = 0; k < qlen % RC; ++k) f *= lam;
+    float* U0 = u_scratch + (((size_t)(q0 / RC + e)) * nH + head) * dk * dv + i;
+    const size_t stride = (size_t)nH * dk * dv;
+    // eight chunks' additions are fetched at once: the walk itself is a chain, the loads need not be
+    for (int c0 = 0; c0 < nc; c0 += 8) {
+        float u[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) u[k] = c0 + k < nc ? U0[(size_t)(c0 + k) * stride] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int c = c0 + k;
+            if (c >= nc) break;
+            U0[(size_t)c * stride] = s;
+            float f = full;
+            if (c == nc - 1 && qlen % RC) {
+                f = 1.f;
+                for (int m = 0; m < qlen % RC; ++m) f *= lam;
+            }
+            s = fmaf(s, f, u[k]);
         }
-        s = fmaf(s, f, u);
     }
     *S = s;
 }

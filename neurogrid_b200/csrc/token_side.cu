@@ -14,9 +14,7 @@ __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-#define TS_THREADS 512
-
-template <int R>
+template <int R, int TS_THREADS>
 __global__ void __launch_bounds__(TS_THREADS)
 token_side_kernel(float* __restrict__ h, const int* __restrict__ tokens, const float* __restrict__ table,
                   const float* __restrict__ w_gate, const float* __restrict__ w_proj_t, const float* __restrict__ w_norm,
@@ -141,18 +139,18 @@ token_side_kernel(float* __restrict__ h, const int* __restrict__ tokens, const f
     }
 }
 
-template <int R>
+template <int R, int TS_THREADS>
 static int token_side_launch(float* h, const int* tokens, const float* table, const float* w_gate, const float* w_proj_t,
                              const float* w_norm, const int* row_entry, int n_rows, int H, int dim, int vocab, float eps,
                              int* status, cudaStream_t stream) {
     const size_t smem = (size_t)R * ((size_t)H + dim) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(token_side_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(token_side_kernel<R, TS_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         configured = true;
     }
-    NG_LAUNCH((token_side_kernel<R>), (n_rows + R - 1) / R, TS_THREADS, smem, stream, h, tokens, table, w_gate, w_proj_t,
+    NG_LAUNCH((token_side_kernel<R, TS_THREADS>), (n_rows + R - 1) / R, TS_THREADS, smem, stream, h, tokens, table, w_gate, w_proj_t,
               w_norm, n_rows, H, dim, vocab, eps, row_entry, status);
     return ng_launch_status();
 }
@@ -164,8 +162,8 @@ NG_EXPORT int ng_token_side(float* h, const int* tokens, const float* table, con
     if (H <= 0 || dim <= 0 || vocab <= 0) return NG_BAD_SIZE;
     const size_t per_row = ((size_t)H + dim) * sizeof(float), cap = 160 * 1024;
     if (per_row > cap) return NG_BAD_SIZE;
-#define TS_GO(RR) return token_side_launch<RR>(h, tokens, table, w_gate, w_proj_t, w_norm, row_entry, n_rows, H, dim, vocab, eps, status, stream)
-    if (n_rows >= 512 && 8 * per_row <= cap) TS_GO(8);
-    if (n_rows >= 128 && 4 * per_row <= cap) TS_GO(4);
-    TS_GO(1);
+#define TS_GO(RR, TT) return token_side_launch<RR, TT>(h, tokens, table, w_gate, w_proj_t, w_norm, row_entry, n_rows, H, dim, vocab, eps, status, stream)
+    if (n_rows >= 512 && 8 * per_row <= cap) TS_GO(8, 512);
+    if (n_rows >= 128 && 4 * per_row <= cap) TS_GO(4, 512);
+    TS_GO(1, 1024);            // few rows: a block's speed is its loads in flight
 }
