@@ -744,7 +744,8 @@ def metanex_kernel_times(eng, l2, pk):
         tok = torch.randint(0, model.spec.vocab_size, (rows,), generator=g, device=dev).to(torch.int32)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         sd = blk.side
-        us = timed(lambda: ops.token_side(h, tok, sd.table, sd.w_gate, sd.w_proj, sd.w_norm, re, sd.spec.eps, status))
+        ssc = torch.empty(max(1, ops.token_side_scratch(rows, D, sd.spec.dim)), device=dev) if rows < 128 else None
+        us = timed(lambda: ops.token_side(h, tok, sd.table, sd.w_gate, sd.w_proj, sd.w_norm, re, sd.spec.eps, status, ssc))
         mem(f"{tag}_token_side", us, 2 * rows * D * 4 + (sd.w_gate.numel() + sd.w_proj.numel()) * 4)
         # router and weighting of the experts' activations
         f = blk.ffn
@@ -767,7 +768,9 @@ def metanex_kernel_times(eng, l2, pk):
         mem(f"{tag}_latent_prep", us, down.numel() * 2 + cq.numel() * 2 + rows * lat.rank_p * 2 + gate.numel() * 4)
         qa = rnd(rows, ls.n_heads * lat.rank_p)
         ao = torch.empty_like(qa)
-        us = timed(lambda: ops.latent_core(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale))
+        nsp = max(1, min(lat.MAX_SPLITS, 128 // rows, ls.window // 64)) if rows <= lat.SPLIT_MAX_ROWS else 1
+        part = torch.empty(max(1, ops.latent_core_partial_floats(rows, ls.n_heads, lat.rank_p, nsp)), device=dev)
+        us = timed(lambda: ops.latent_core(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale, nsp, part))
         keys = min(ls.window, 2048 + q)
         flops = 4 * rows * ls.n_heads * keys * lat.rank_p
         out[f"{tag}_latent_attention_core"] = {"us": round(us, 2), "fp32_flops": int(flops),

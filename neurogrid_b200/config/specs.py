@@ -175,8 +175,8 @@ class LatentAttentionSpec:
     def __post_init__(self):
         if self.window is not None and self.window < 1:
             raise ValueError("attention window must be >= 1")
-        if not (1 <= self.kv_rank <= 256):
-            raise ValueError(f"latent attention: kv_rank must be in [1, 256], got {self.kv_rank}")
+        if not (1 <= self.kv_rank <= 512):
+            raise ValueError(f"latent attention: kv_rank must be in [1, 512], got {self.kv_rank}")
 
 
 @dataclass(frozen=True)

@@ -13,7 +13,7 @@
 #include "ng_common.cuh"
 
 #define AG_WARPS 4
-#define AG_MAX_J 8      // head_dim <= 256
+#define AG_MAX_J 16     // head_dim <= 512
 
 template <typename T>
 __global__ void __launch_bounds__(AG_WARPS * 32)

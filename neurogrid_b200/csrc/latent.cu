@@ -77,7 +77,8 @@ template <typename T, int HPW, int NJ>
 __global__ void __launch_bounds__(512)
 latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const int* __restrict__ table, int table_stride,
                    const int* __restrict__ positions, const int* __restrict__ row_entry, const float* __restrict__ gate,
-                   T* __restrict__ out, int nH, int rp, int page_size, int num_pages, int window, float scale) {
+                   T* __restrict__ out, int nH, int rp, int page_size, int num_pages, int window, float scale,
+                   int n_splits, float* __restrict__ partial) {
     extern __shared__ float sm[];
     const int ldt = rp + 1;
     float* Ts = sm;                        // [LC_TILE][rp+1]
@@ -92,8 +93,14 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
         for (int i = tid; i < nH * rp; i += blockDim.x) ng_st(orow + i, 0.f);
         return;
     }
-    const int pos = positions[row];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int pos_row = positions[row];
+    const int lo_row = window > 0 ? max(0, pos_row - window + 1) : 0;
+    // with n_splits > 1 the row's tiles are dealt to n_splits blocks in runs; each leaves its running maximum, sum
+    // and weighted sum in `partial` and a second kernel merges the runs in ascending order
+    const int tiles = (pos_row - lo_row + LC_TILE) / LC_TILE;
+    const int per = (tiles + n_splits - 1) / n_splits;
+    const int lo = lo_row + (int)blockIdx.y * per * LC_TILE;
+    const int pos = min(pos_row, lo + per * LC_TILE - 1);          // lo > pos: this block has no keys
     const int* trow = table + (size_t)entry * table_stride;
     for (int i = tid; i < nH * rp; i += blockDim.x) qs[i] = ng_ld(q + (size_t)row * nH * rp + i) * scale;
     float m[HPW], l[HPW], acc[HPW][NJ];
@@ -124,7 +131,7 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
             }
         }
     };
-    fetch(lo);
+    if (lo <= pos) fetch(lo);
     for (int k0 = lo; k0 <= pos; k0 += LC_TILE) {
         const int n = min(LC_TILE, pos + 1 - k0);
         __syncthreads();
@@ -182,6 +189,19 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
     for (int u = 0; u < HPW; ++u) {
         const int head = warp + u * nwarp;
         if (head >= nH) break;
+        if (n_splits > 1) {
+            float* dst = partial + (((size_t)row * nH + head) * n_splits + blockIdx.y) * (rp + 2);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int d = lane + 32 * j;
+                if (d < rp) dst[d] = acc[u][j];
+            }
+            if (lane == 0) {
+                dst[rp] = m[u];
+                dst[rp + 1] = l[u];
+            }
+            continue;
+        }
         const float f = (l[u] > 0.f ? 1.f / l[u] : 0.f) * (gate ? gate[(size_t)row * nH + head] : 1.f);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -191,12 +211,47 @@ latent_core_kernel(const T* __restrict__ q, const T* __restrict__ pages, const i
     }
 }
 
+// merges the runs of a (row, head) in ascending order: a warp each
+template <typename T>
+__global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ gate,
+                                    const int* __restrict__ row_entry, T* __restrict__ out, int n_rows, int nH, int rp,
+                                    int n_splits) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= n_rows * nH) return;
+    const int row = w / nH;
+    if (row_entry[row] < 0) return;                 // the core wrote zeros there
+    const float* src = partial + (size_t)w * n_splits * (rp + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, src[(size_t)s * (rp + 2) + rp]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = src[(size_t)s * (rp + 2) + rp];
+        if (ms > -INFINITY) L += src[(size_t)s * (rp + 2) + rp + 1] * expf(ms - M);
+    }
+    const float f = (L > 0.f ? 1.f / L : 0.f) * (gate ? gate[w] : 1.f);
+    for (int d = lane; d < rp; d += 32) {
+        float a = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = src[(size_t)s * (rp + 2) + rp];
+            if (ms > -INFINITY) a += src[(size_t)s * (rp + 2) + d] * expf(ms - M);
+        }
+        ng_st(out + (size_t)w * rp + d, a * f);
+    }
+}
+
 // q, out: [n_rows, nH*rp]; pages: [num_pages, 1, page_size, rp]; gate: float32 [n_rows, nH] or null.
+// `n_splits` > 1: every row's keys are cut into that many runs, each a block of its own (steps of few rows);
+// `partial` then holds n_rows * nH * n_splits * (rp + 2) float32 values.
 NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table, int table_stride, const int* positions,
                              const int* row_entry, const float* gate, void* out, int n_rows, int nH, int rp, int page_size,
-                             int num_pages, int window, float scale, int act_bf16, cudaStream_t stream) {
+                             int num_pages, int window, float scale, int n_splits, float* partial, int act_bf16,
+                             cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (nH <= 0 || rp <= 0 || rp > 32 * LC_MAX_J || page_size <= 0 || nH > 64) return NG_BAD_SIZE;
+    if (nH <= 0 || rp <= 0 || rp > 32 * LC_MAX_J || page_size <= 0 || nH > 64 || n_splits < 1 || n_splits > 64 ||
+        (n_splits > 1 && !partial))
+        return NG_BAD_SIZE;
     const int nwarp = nH <= 8 ? 8 : nH <= 16 ? nH : 16;           // at least 256 threads: all of them fetch the tiles
     const int hpw = (nH + nwarp - 1) / nwarp;
     const size_t smem = ((size_t)LC_TILE * (rp + 1) + (size_t)nH * rp) * sizeof(float);
@@ -210,9 +265,9 @@ NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table,
                 return NG_LAUNCH_FAILED;                                                                               \
             configured = true;                                                                                         \
         }                                                                                                              \
-        NG_LAUNCH((latent_core_kernel<TT, HH, JJ>), n_rows, nwarp * 32, smem, stream, (const TT*)q, (const TT*)pages,  \
-                  table, table_stride, positions, row_entry, gate, (TT*)out, nH, rp, page_size, num_pages, window,     \
-                  scale);                                                                                              \
+        NG_LAUNCH((latent_core_kernel<TT, HH, JJ>), dim3(n_rows, n_splits), nwarp * 32, smem, stream, (const TT*)q,   \
+                  (const TT*)pages, table, table_stride, positions, row_entry, gate, (TT*)out, nH, rp, page_size,      \
+                  num_pages, window, scale, n_splits, partial);                                                        \
     }
     // columns a lane keeps of a head's sum: the smallest of 1, 2, 4, 8 that covers the latent
 #define LC_BY_J(TT, HH)                                                                                                \
@@ -224,6 +279,15 @@ NG_EXPORT int ng_latent_core(const void* q, const void* pages, const int* table,
         if (hpw == 1) LC_BY_J(__nv_bfloat16, 1) else if (hpw == 2) LC_BY_J(__nv_bfloat16, 2) else LC_BY_J(__nv_bfloat16, 4)
     } else {
         if (hpw == 1) LC_BY_J(float, 1) else if (hpw == 2) LC_BY_J(float, 2) else LC_BY_J(float, 4)
+    }
+    if (n_splits > 1) {
+        const unsigned blocks = (unsigned)(((size_t)n_rows * nH + 7) / 8);
+        if (act_bf16)
+            NG_LAUNCH((latent_merge_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (const float*)partial, gate, row_entry,
+                      (__nv_bfloat16*)out, n_rows, nH, rp, n_splits);
+        else
+            NG_LAUNCH((latent_merge_kernel<float>), blocks, 256, 0, stream, (const float*)partial, gate, row_entry,
+                      (float*)out, n_rows, nH, rp, n_splits);
     }
     return ng_launch_status();
 }

@@ -85,6 +85,36 @@ __global__ void moe_scale_kernel(T* __restrict__ act, const float* __restrict__ 
     ng_st(p, ng_ld(p) * weights[(size_t)row * E + c / ff]);
 }
 
+// out[row, c] = silu(gate_up[row, c]) * gate_up[row, I + c] * (c < E*ff ? weights[row, c / ff] : 1): the SwiGLU of all
+// experts side by side with the routing weight applied at once (steps whose gate/up product has no fused epilogue)
+template <typename T>
+__global__ void moe_swiglu_scaled_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights,
+                                         T* __restrict__ out, int I, int E, int ff) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= I) return;
+    const float g = ng_ld(gate_up + (size_t)row * 2 * I + c), u = ng_ld(gate_up + (size_t)row * 2 * I + I + c);
+    T act;
+    ng_st(&act, g / (1.f + expf(-g)) * u);           // rounded as the unweighted activation is, then weighted
+    const float w = c < E * ff ? weights[(size_t)row * E + c / ff] : 1.f;
+    ng_st(out + (size_t)row * I + c, ng_ld(&act) * w);
+}
+
+NG_EXPORT int ng_moe_swiglu_scaled(const void* gate_up, const float* weights, void* out, int n_rows, int I, int E, int ff,
+                                   int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (E <= 0 || ff <= 0 || I < E * ff || n_rows > 65535) return NG_BAD_SIZE;
+    dim3 grid((I + 255) / 256, n_rows);
+    if (act_bf16)
+        NG_LAUNCH((moe_swiglu_scaled_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gate_up, weights,
+                  (__nv_bfloat16*)out, I, E, ff);
+    else
+        NG_LAUNCH((moe_swiglu_scaled_kernel<float>), grid, 256, 0, stream, (const float*)gate_up, weights, (float*)out, I, E, ff);
+    return ng_launch_status();
+}
+
 NG_EXPORT int ng_moe_router(const void* x, const float* wr, const float* br, float* weights, int n_rows, int H,
                             int E, int top_k, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;

@@ -452,19 +452,29 @@ def latent_core_takes(n_heads: int, rank: int) -> bool:
 
 def latent_core(q: torch.Tensor, pages: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
                 row_entry: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_heads: int,
-                window: Optional[int], scale: float) -> None:
+                window: Optional[int], scale: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
     """out[N, nH*r] = gate[N, nH] * softmax(q_h . c_j * scale over the visible j) c_j, every head reading the same
-    latent pages[P, 1, page, r] as keys and as values; float32 scores, weights and sums."""
+    latent pages[P, 1, page, r] as keys and as values; float32 scores, weights and sums.  ``n_splits`` > 1 cuts every
+    row's keys into that many runs, each a block of its own, merged through ``partial`` (float32,
+    ``latent_core_partial_floats`` values): for steps of few rows."""
     n = q.shape[0]
     num_pages, one, page_size, rp = pages.shape
     if q.shape != (n, n_heads * rp) or out.shape != q.shape or one != 1 or q.dtype != pages.dtype or out.dtype != q.dtype \
             or (gate is not None and gate.shape != (n, n_heads)):
         raise KernelError("latent_core: shapes or dtypes do not fit")
     _f32(gate, "gate"), _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
-    f = _fn("latent", "ng_latent_core", [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 6 + [_c_float, _c_int, _c_void_p])
+    _f32(partial, "partial")
+    if n_splits > 1 and (partial is None or partial.numel() < latent_core_partial_floats(n, n_heads, rp, n_splits)):
+        raise KernelError("latent_core: the runs need latent_core_partial_floats float32 values")
+    f = _fn("latent", "ng_latent_core", [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 6
+            + [_c_float, _c_int, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(q), _ptr(pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry), _ptr(gate), _ptr(out),
-             n, n_heads, rp, page_size, num_pages, int(window or 0), float(scale), _act_flag(q, "q"), _stream()),
-           "latent_core")
+             n, n_heads, rp, page_size, num_pages, int(window or 0), float(scale), int(n_splits),
+             _ptr(partial) if n_splits > 1 else None, _act_flag(q, "q"), _stream()), "latent_core")
+
+
+def latent_core_partial_floats(n_rows: int, n_heads: int, rank: int, n_splits: int) -> int:
+    return n_rows * n_heads * n_splits * (rank + 2) if n_splits > 1 else 0
 
 
 def head_gate(y: torch.Tensor, gate: torch.Tensor, n_heads: int) -> None:
@@ -502,22 +512,42 @@ def moe_scale(act: torch.Tensor, weights: torch.Tensor, expert_ff: int) -> None:
     _check(f(_ptr(act), _ptr(weights), n, E, int(expert_ff), ld, _act_flag(act, "moe act"), _stream()), "moe_scale")
 
 
+def moe_swiglu_scaled(gate_up: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, expert_ff: int) -> None:
+    """out[N, I] = silu(gate_up[:, :I]) * gate_up[:, I:], columns e*ff..(e+1)*ff times weights[N, e] (float32)."""
+    n, I = out.shape
+    E = weights.shape[1]
+    if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype or weights.shape[0] != n or I < E * expert_ff:
+        raise KernelError("moe_swiglu_scaled: shapes do not fit")
+    _f32(weights, "routing weights")
+    f = _fn("moe", "ng_moe_swiglu_scaled", [_c_void_p] * 3 + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(gate_up), _ptr(weights), _ptr(out), n, I, E, int(expert_ff), _act_flag(out, "moe act"), _stream()),
+           "moe_swiglu_scaled")
+
+
 # ----------------------------------------------------------------------------- per-layer token input
 def token_side(h: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, w_gate: torch.Tensor,
                w_proj: torch.Tensor, w_norm: torch.Tensor, row_entry: torch.Tensor, eps: float,
-               status: torch.Tensor) -> None:
+               status: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> None:
     """h[N,H] float32 += rmsnorm(W_proj (gelu_tanh(W_gate h) * table[tokens])) * w_norm; all float32.
-    ``w_proj`` is given transposed, [dim, H]."""
+    ``w_proj`` is given transposed, [dim, H].  ``scratch`` (float32, ``token_side_scratch`` values): steps of few
+    rows deal the same sums to many blocks through it; without it a block takes whole rows."""
     n, H = h.shape
     V, dim = table.shape
     if w_gate.shape != (dim, H) or w_proj.shape != (dim, H) or w_norm.numel() != H:
         raise KernelError("token_side: shapes do not fit")
     for t, what in ((h, "residual stream"), (table, "token table"), (w_gate, "gate"), (w_proj, "proj"), (w_norm, "norm")):
         _f32(t, what)
-    _i32(tokens, "tokens"), _i32(row_entry, "row_entry"), _i32(status, "status")
-    f = _fn("token_side", "ng_token_side", [_c_void_p] * 7 + [_c_int] * 4 + [_c_float, _c_void_p, _c_void_p])
+    _i32(tokens, "tokens"), _i32(row_entry, "row_entry"), _i32(status, "status"), _f32(scratch, "scratch")
+    if scratch is not None and scratch.numel() < token_side_scratch(n, H, dim):
+        raise KernelError("token_side: the scratch is too small")
+    f = _fn("token_side", "ng_token_side", [_c_void_p] * 7 + [_c_int] * 4 + [_c_float, _c_void_p, _c_void_p, _c_void_p])
     _check(f(_ptr(h), _ptr(tokens), _ptr(table), _ptr(w_gate), _ptr(w_proj), _ptr(w_norm), _ptr(row_entry), n, H, dim, V,
-             float(eps), _ptr(status), _stream()), "token_side")
+             float(eps), _ptr(status), _ptr(scratch), _stream()), "token_side")
+
+
+def token_side_scratch(n_rows: int, H: int, dim: int) -> int:
+    """float32 values of scratch with which a step of ``n_rows`` rows runs the few-rows kernels (0: none needed)."""
+    return n_rows * (dim + H + (H + 127) // 128) if n_rows < 128 else 0
 
 
 # ----------------------------------------------------------------------------- sampling

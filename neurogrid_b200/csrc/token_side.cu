@@ -155,11 +155,98 @@ static int token_side_launch(float* h, const int* tokens, const float* table, co
     return ng_launch_status();
 }
 
+// ---------------------------------------------------------------------------------------------- steps of few rows
+// A block per row would leave most of the GPU idle and stream both matrices through one SM, so the same sums
+// are dealt to many blocks: `gate` forms eight gate values a block (a warp each, the same walk as above),
+// `proj` forms y for 128 columns a block and the partial sum of their squares, `apply` adds up the partial
+// sums in ascending order and adds the normed y into the stream.  `scratch`: g [n_rows, dim], y [n_rows, H],
+// partial sums [n_rows, ceil(H / 128)], float32.
+__global__ void __launch_bounds__(256)
+token_side_gate_kernel(const float* __restrict__ h, const int* __restrict__ tokens, const float* __restrict__ table,
+                       const float* __restrict__ w_gate, float* __restrict__ g, int H, int dim, int vocab,
+                       const int* __restrict__ row_entry, int* __restrict__ status) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.y, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= dim || row_entry[row] < 0) return;
+    int tok = tokens[row];
+    if (tok < 0 || tok >= vocab) {
+        if (lane == 0) atomicOr(status, NG_STATUS_BAD_TOKEN);
+        tok = 0;
+    }
+    const float* x = h + (size_t)row * H;
+    const float* w = w_gate + (size_t)i * H;
+    float acc = 0.f;
+    if (H % 4 == 0) {
+#pragma unroll 4
+        for (int j = lane * 4; j < H; j += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + j), xv = *reinterpret_cast<const float4*>(x + j);
+            acc = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc))));
+        }
+    } else {
+        for (int j = lane; j < H; j += 32) acc = fmaf(x[j], w[j], acc);
+    }
+    acc = ng_warp_sum(acc);
+    if (lane == 0) g[(size_t)row * dim + i] = gelu_tanh(acc) * table[(size_t)tok * dim + i];
+}
+
+__global__ void __launch_bounds__(128)
+token_side_proj_kernel(const float* __restrict__ g, const float* __restrict__ w_proj_t, float* __restrict__ y,
+                       float* __restrict__ ss_part, int H, int dim, int n_slices, const int* __restrict__ row_entry) {
+    __shared__ float red[32];
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.y;
+    if (row_entry[row] < 0) return;
+    const int j = blockIdx.x * 128 + threadIdx.x;
+    const float* gr = g + (size_t)row * dim;
+    float acc = 0.f;
+    if (j < H) {
+#pragma unroll 8
+        for (int i = 0; i < dim; ++i) acc = fmaf(w_proj_t[(size_t)i * H + j], gr[i], acc);
+        y[(size_t)row * H + j] = acc;
+    }
+    const float ss = ng_block_sum(acc * acc, red);
+    if (threadIdx.x == 0) ss_part[(size_t)row * n_slices + blockIdx.x] = ss;
+}
+
+__global__ void __launch_bounds__(256)
+token_side_apply_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ ss_part,
+                        const float* __restrict__ w_norm, int H, int n_slices, float eps, const int* __restrict__ row_entry) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    if (row_entry[row] < 0) return;
+    float ss = 0.f;
+    for (int k = 0; k < n_slices; ++k) ss += ss_part[(size_t)row * n_slices + k];
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) h[(size_t)row * H + j] += y[(size_t)row * H + j] * r * w_norm[j];
+}
+
+// float32 values of scratch the few-rows path needs (0: the step is long enough for the fused kernel)
+NG_EXPORT long long ng_token_side_scratch(int n_rows, int H, int dim) {
+    return n_rows < 128 ? (long long)n_rows * ((long long)dim + H + (H + 127) / 128) : 0;
+}
+
 NG_EXPORT int ng_token_side(float* h, const int* tokens, const float* table, const float* w_gate, const float* w_proj_t,
                             const float* w_norm, const int* row_entry, int n_rows, int H, int dim, int vocab, float eps,
-                            int* status, cudaStream_t stream) {
+                            int* status, float* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (H <= 0 || dim <= 0 || vocab <= 0) return NG_BAD_SIZE;
+    if (scratch && n_rows < 128) {
+        const int n_slices = (H + 127) / 128;
+        float* g = scratch;
+        float* y = g + (size_t)n_rows * dim;
+        float* part = y + (size_t)n_rows * H;
+        NG_LAUNCH((token_side_gate_kernel), dim3((dim + 7) / 8, n_rows), 256, 0, stream, (const float*)h, tokens, table, w_gate,
+                  g, H, dim, vocab, row_entry, status);
+        NG_LAUNCH((token_side_proj_kernel), dim3(n_slices, n_rows), 128, 0, stream, (const float*)g, w_proj_t, y, part, H, dim,
+                  n_slices, row_entry);
+        NG_LAUNCH((token_side_apply_kernel), n_rows, 256, 0, stream, h, (const float*)y, (const float*)part, w_norm, H,
+                  n_slices, eps, row_entry);
+        return ng_launch_status();
+    }
     const size_t per_row = ((size_t)H + dim) * sizeof(float), cap = 160 * 1024;
     if (per_row > cap) return NG_BAD_SIZE;
 #define TS_GO(RR, TT) return token_side_launch<RR, TT>(h, tokens, table, w_gate, w_proj_t, w_norm, row_entry, n_rows, H, dim, vocab, eps, status, stream)

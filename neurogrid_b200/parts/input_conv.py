@@ -70,5 +70,9 @@ class TokenSide:
         return [("token_side", None)]
 
     def forward(self, h, ctx):
+        s = self.spec
+        need = ops.token_side_scratch(h.shape[0], s.hidden, s.dim)
+        scratch = ctx.ws.flat("side_scratch", need, torch.float32,
+                              reserve=ops.token_side_scratch(127, s.hidden, s.dim)) if need else None
         ops.token_side(h, ctx.tokens, self.table, self.w_gate, self.w_proj, self.w_norm, ctx.row_entry,
-                       self.spec.eps, ctx.status)
+                       s.eps, ctx.status, scratch)

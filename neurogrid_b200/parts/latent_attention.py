@@ -25,6 +25,8 @@ class LatentAttention:
     norms and the gate are float32 too."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    SPLIT_MAX_ROWS = 32    # steps of up to this many rows cut each row's keys into runs
+    MAX_SPLITS = 16
 
     def __init__(self, spec, *, dtype, device, owns_cache=True):
         if not owns_cache:
@@ -82,8 +84,17 @@ class LatentAttention:
         ops.linear(cq, self.w_q, None, q)
         o = ctx.ws.buf("lat_o", n, H * rp, self.dtype)
         if ops.latent_core_takes(H, rp):
+            # a step of few rows has too few blocks for the GPU: every row's keys are cut into runs, a block each
+            n_splits = 1
+            if n <= self.SPLIT_MAX_ROWS:
+                longest = s.window or cache.table.shape[1] * cache.k_pages.shape[2]
+                n_splits = max(1, min(self.MAX_SPLITS, 128 // n, longest // 64))
+            partial = None
+            if n_splits > 1:
+                partial = ctx.ws.flat("lat_partial", ops.latent_core_partial_floats(n, H, rp, n_splits), torch.float32,
+                                      reserve=ops.latent_core_partial_floats(self.SPLIT_MAX_ROWS, H, rp, self.MAX_SPLITS))
             ops.latent_core(q, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, gate, o, H, s.window,
-                            s.softmax_scale)
+                            s.softmax_scale, n_splits, partial)
         else:                                   # very many heads or a very wide latent: the plain kernel, then the gate
             ops.attention_generic(q, cache.k_pages, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, o,
                                   H, s.window, s.softmax_scale)

@@ -63,9 +63,9 @@ class MoE:
         act = ctx.ws.buf("moe_act", n, I, self.dtype)
         if ops.gemm_sm100_ok(x, self.w_gate_up):
             ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the epilogue
+            ops.moe_scale(act, weights, s.expert_ff)
         else:
             gu = ctx.ws.buf("moe_gate_up", n, 2 * I, self.dtype)
             ops.linear(x, self.w_gate_up, None, gu)
-            ops.swiglu(gu, act)
-        ops.moe_scale(act, weights, s.expert_ff)
+            ops.moe_swiglu_scaled(gu, weights, act, s.expert_ff)   # gate and routing weight in one pass
         return ops.linear_to_residual(act, self.w_down, None, ctx.ws, "ffn_out", residual=ctx.residual)

@@ -298,17 +298,19 @@ def test_moe(dtype, experts, top, ff, shared):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_token_side(dtype):
-    H, dim, V, layer, n_layers = 88, 6, 50, 2, 4
+@pytest.mark.parametrize("rows,H", [(11, 88), (11, 333), (200, 88), (600, 70)])
+def test_token_side(dtype, rows, H):
+    """Few rows (the sums dealt to many blocks), and steps long enough for blocks of four and of eight rows."""
+    dim, V, layer, n_layers = 6, 50, 2, 4
     spec = TokenSideSpec(H, dim, layer * dim, "side.embed", n_layers * dim, V, 1e-5)
     part = TokenSide(spec, dtype=dtype, device=DEV)
     w = _mats({"gate": (dim, H), "proj": (H, dim), "norm": (H,)}, 8)
     table = _mats({"side.embed": (V, n_layers * dim)}, 9)
     part.bind(w)
     part.bind_shared(table)
-    h = _x(11, H, torch.float32, scale=2.0)
-    ctx = make_ctx([11], [0], [0], dtype=dtype)
-    toks = torch.randint(0, V, (11,), generator=torch.Generator().manual_seed(1))
+    h = _x(rows, H, torch.float32, scale=2.0)
+    ctx = make_ctx([rows], [0], [0], dtype=dtype)
+    toks = torch.randint(0, V, (rows,), generator=torch.Generator().manual_seed(1))
     ctx.tokens = toks.to(torch.int32).to(DEV)
     pw = {f"l{layer}.side." + k: v.double() for k, v in w.items()}
     pw["side.embed"] = table["side.embed"].double()
