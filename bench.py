@@ -770,7 +770,10 @@ def metanex_kernel_times(eng, l2, pk):
         ao = torch.empty_like(qa)
         nsp = max(1, min(lat.MAX_SPLITS, 128 // rows, ls.window // 64)) if rows <= lat.SPLIT_MAX_ROWS else 1
         part = torch.empty(max(1, ops.latent_core_partial_floats(rows, ls.n_heads, lat.rank_p, nsp)), device=dev)
-        us = timed(lambda: ops.latent_core(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale, nsp, part))
+        if rows > lat.SPLIT_MAX_ROWS and ops.latent_core_mma_takes(ls.n_heads, lat.rank_p, torch.bfloat16):
+            us = timed(lambda: ops.latent_core_mma(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale))
+        else:
+            us = timed(lambda: ops.latent_core(qa, pages, table, pos, re, gate, ao, ls.n_heads, ls.window, ls.softmax_scale, nsp, part))
         keys = min(ls.window, 2048 + q)
         flops = 4 * rows * ls.n_heads * keys * lat.rank_p
         out[f"{tag}_latent_attention_core"] = {"us": round(us, 2), "fp32_flops": int(flops),

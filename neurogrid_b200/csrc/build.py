@@ -35,7 +35,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "attention_generic": (), "sampling": (), "attention_bf16": (),
     "gemm_sm100": (),
     "attention_sm100": (),
-    "input_conv": (), "retention": (), "latent": (), "moe": (), "token_side": (),
+    "input_conv": (), "retention": (), "latent": (), "latent_mma": (), "moe": (), "token_side": (),
 }
 
 _lock = threading.RLock()
@@ -179,4 +179,4 @@ def build_all(extra: Sequence[Tuple[str, Mapping[str, object]]] = (), *, verbose
 
 # sources that only exist as ``-D`` specialisations (never built bare)
 SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",), "shortconv": ("NG_CONV_L",),
-                                         "rope_cache": ("NG_ROPE_PAIRS",)}
+                                         "rope_cache": ("NG_ROPE_PAIRS",), "latent_mma": ("NG_LAT_RANK",)}

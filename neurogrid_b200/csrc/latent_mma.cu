@@ -1,0 +1,223 @@
+// Latent attention core for long steps (bfloat16) on the tensor cores, with float32 scores, weights and sums.
+//
+// Every head of a row reads the same latent pages as keys and as values, so the heads of ONE row are the 16
+// rows of an m16n8k16 tile: a warp takes a row, stages 32 latents at a time in shared memory (16-byte loads),
+// and forms
+//     S[16 heads x 32 keys] = Q C^T      bfloat16 x bfloat16 products are exact, the sum is float32: float32 scores
+//     online softmax in float32 (a quad of lanes holds a head's 32 scores)
+//     O[16 heads x rank]   += P C        with the float32 weights P cut into three bfloat16 terms hi + mid + lo
+//                                        (p - hi - mid - lo is below 2^-24 p): each term's products are exact
+//                                        in the float32 accumulators, so the weighted sum is a float32 sum
+// The head's gate multiplies the result in the store.  Up to 16 heads (rows of the tile past the heads are zero),
+// rank a multiple of 32 fixed at compile time (-DNG_LAT_RANK).  Keys are walked in ascending order from the
+// window's first key: a row's result does not depend on the cut or the batch.
+#include "ng_common.cuh"
+
+#ifndef NG_LAT_RANK
+#error "compile with -DNG_LAT_RANK=<padded latent width, a multiple of 32 up to 256>"
+#endif
+static_assert(NG_LAT_RANK % 32 == 0 && NG_LAT_RANK >= 32 && NG_LAT_RANK <= 256, "latent width: a multiple of 32 up to 256");
+
+#define LM_R NG_LAT_RANK
+#define LM_TILE 32
+#if NG_LAT_RANK > 160
+#define LM_WARPS 2                // the warps' tiles share 48 KB of static shared memory
+#else
+#define LM_WARPS 4
+#endif
+#define LM_LD (LM_R + 8)          // shared-memory row in elements: 16 bytes of padding keep ldmatrix off one bank
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void lm_ldsm4(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldsm4_t(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack(float x, float y) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+// (x, y) as three bfloat16 pairs whose sum is (x, y) to float32 accuracy
+__device__ __forceinline__ void lm_split3(float x, float y, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+    const bf16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+    const float xr = x - __bfloat162float(xh), yr = y - __bfloat162float(yh);
+    const bf16 xm = __float2bfloat16_rn(xr), ym = __float2bfloat16_rn(yr);
+    hi = lm_pack(__bfloat162float(xh), __bfloat162float(yh));
+    mid = lm_pack(__bfloat162float(xm), __bfloat162float(ym));
+    lo = lm_pack(xr - __bfloat162float(xm), yr - __bfloat162float(ym));
+}
+
+__global__ void __launch_bounds__(LM_WARPS * 32)
+latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages, const int* __restrict__ table,
+                       int table_stride, const int* __restrict__ positions, const int* __restrict__ row_entry,
+                       const float* __restrict__ gate, bf16* __restrict__ out, int n_rows, int nH, int page_size,
+                       int num_pages, int window, float scale) {
+    __shared__ __align__(16) bf16 tiles[LM_WARPS][LM_TILE * LM_LD];
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * LM_WARPS + warp;
+    if (row >= n_rows) return;
+    const int quad = lane >> 2, tq = lane & 3;             // heads quad and quad + 8; columns 2 tq, 2 tq + 1 of an 8-wide tile
+    bf16* orow = out + (size_t)row * nH * LM_R;
+    const int entry = row_entry[row];
+    if (entry < 0) {
+        for (int i = lane; i < nH * LM_R; i += 32) orow[i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = positions[row];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* trow = table + (size_t)entry * table_stride;
+    bf16* tile = tiles[warp];
+
+    // the row's queries as A fragments: heads quad and quad + 8, all of the latent's columns
+    uint32_t qa[LM_R / 16][4];
+    {
+        const bf16* q0 = q + ((size_t)row * nH + quad) * LM_R;
+        const bf16* q1 = q0 + (size_t)8 * LM_R;
+        const bool h0 = quad < nH, h1 = quad + 8 < nH;
+#pragma unroll
+        for (int ks = 0; ks < LM_R / 16; ++ks) {
+            const int d = ks * 16 + tq * 2;
+            qa[ks][0] = h0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+            qa[ks][1] = h1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+            qa[ks][2] = h0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+            qa[ks][3] = h1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+        }
+    }
+    float o[LM_R / 8][4];
+#pragma unroll
+    for (int t = 0; t < LM_R / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    constexpr int CPK = LM_R / 8;                              // 16-byte pieces of a key
+    for (int k0 = lo; k0 <= pos; k0 += LM_TILE) {
+        const int n = min(LM_TILE, pos + 1 - k0);
+        __syncwarp();
+        // stage the tile: keys past the row's last are zero
+#pragma unroll
+        for (int i = 0; i < CPK; ++i) {
+            const int c = lane + 32 * i;
+            const int k = c / CPK, part = c % CPK;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (k < n) {
+                const int kp = k0 + k;
+                const int page = trow[kp / page_size];
+                if (page >= 0 && page < num_pages)
+                    v = *reinterpret_cast<const uint4*>(pages + ((size_t)page * page_size + (kp % page_size)) * LM_R + part * 8);
+            }
+            *reinterpret_cast<uint4*>(tile + k * LM_LD + part * 8) = v;
+        }
+        __syncwarp();
+        // scores: four tiles of 8 keys
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < LM_R / 16; ks += 2) {
+                uint32_t b[4];                                  // (ks: columns 0-7, 8-15), (ks + 1: columns 0-7, 8-15) of these 8 keys
+                lm_ldsm4(b, tile + (nt * 8 + (lane & 7)) * LM_LD + ks * 16 + (lane >> 3) * 8);
+                lm_mma(s[nt], qa[ks], b[0], b[1]);
+                lm_mma(s[nt], qa[ks + 1], b[2], b[3]);
+            }
+        }
+        // online softmax of heads quad (values 0, 1 of a tile) and quad + 8 (values 2, 3)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const bool ok = nt * 8 + tq * 2 + e < n;
+                s[nt][e] = ok ? s[nt][e] * scale : -INFINITY;
+                s[nt][2 + e] = ok ? s[nt][2 + e] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);      // finite: key k0 is always visible
+        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+        m0 = mn0;
+        m1 = mn1;
+        float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                s[nt][e] = expf(s[nt][e] - mn0);
+                s[nt][2 + e] = expf(s[nt][2 + e] - mn1);
+                r0 += s[nt][e];
+                r1 += s[nt][2 + e];
+            }
+        }
+        l0 = l0 * c0 + r0;                                       // a lane's share; the quad's shares are added at the end
+        l1 = l1 * c1 + r1;
+#pragma unroll
+        for (int t = 0; t < LM_R / 8; ++t) {
+            o[t][0] *= c0;
+            o[t][1] *= c0;
+            o[t][2] *= c1;
+            o[t][3] *= c1;
+        }
+        // weighted sum: two steps of 16 keys, the weights as three bfloat16 terms
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t ph[4], pm[4], pl[4];
+            lm_split3(s[2 * kk][0], s[2 * kk][1], ph[0], pm[0], pl[0]);
+            lm_split3(s[2 * kk][2], s[2 * kk][3], ph[1], pm[1], pl[1]);
+            lm_split3(s[2 * kk + 1][0], s[2 * kk + 1][1], ph[2], pm[2], pl[2]);
+            lm_split3(s[2 * kk + 1][2], s[2 * kk + 1][3], ph[3], pm[3], pl[3]);
+#pragma unroll
+            for (int dt = 0; dt < LM_R / 8; dt += 2) {
+                uint32_t b[4];                                  // (dt: keys 0-7, 8-15), (dt + 1: keys 0-7, 8-15) of this step
+                lm_ldsm4_t(b, tile + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LM_LD + (dt + (lane >> 4)) * 8);
+                lm_mma(o[dt], pl, b[0], b[1]);                  // smallest terms first
+                lm_mma(o[dt], pm, b[0], b[1]);
+                lm_mma(o[dt], ph, b[0], b[1]);
+                lm_mma(o[dt + 1], pl, b[2], b[3]);
+                lm_mma(o[dt + 1], pm, b[2], b[3]);
+                lm_mma(o[dt + 1], ph, b[2], b[3]);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int h0 = quad, h1 = quad + 8;
+    const float f0 = h0 < nH ? (l0 > 0.f ? 1.f / l0 : 0.f) * (gate ? gate[(size_t)row * nH + h0] : 1.f) : 0.f;
+    const float f1 = h1 < nH ? (l1 > 0.f ? 1.f / l1 : 0.f) * (gate ? gate[(size_t)row * nH + h1] : 1.f) : 0.f;
+#pragma unroll
+    for (int t = 0; t < LM_R / 8; ++t) {
+        const int d = t * 8 + tq * 2;
+        if (h0 < nH) *reinterpret_cast<uint32_t*>(orow + (size_t)h0 * LM_R + d) = lm_pack(o[t][0] * f0, o[t][1] * f0);
+        if (h1 < nH) *reinterpret_cast<uint32_t*>(orow + (size_t)h1 * LM_R + d) = lm_pack(o[t][2] * f1, o[t][3] * f1);
+    }
+}
+
+// q, out: bfloat16 [n_rows, nH * NG_LAT_RANK]; pages: bfloat16 [num_pages, 1, page_size, NG_LAT_RANK]; gate float32 or null
+NG_EXPORT int ng_latent_core_mma(const void* q, const void* pages, const int* table, int table_stride, const int* positions,
+                                 const int* row_entry, const float* gate, void* out, int n_rows, int nH, int rp,
+                                 int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (rp != LM_R || nH <= 0 || nH > 16 || page_size <= 0) return NG_BAD_SIZE;
+    NG_LAUNCH((latent_core_mma_kernel), (n_rows + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, 0, stream, (const bf16*)q,
+              (const bf16*)pages, table, table_stride, positions, row_entry, gate, (bf16*)out, n_rows, nH, page_size, num_pages,
+              window, scale);
+    return ng_launch_status();
+}

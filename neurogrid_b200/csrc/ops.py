@@ -473,6 +473,32 @@ def latent_core(q: torch.Tensor, pages: torch.Tensor, table: torch.Tensor, posit
              _ptr(partial) if n_splits > 1 else None, _act_flag(q, "q"), _stream()), "latent_core")
 
 
+LATENT_BACKEND = os.environ.get("NEUROGRID_B200_LATENT", "mma")     # "mma": tensor-core core for long bfloat16 steps; "ffma"
+
+
+def latent_core_mma_takes(n_heads: int, rank: int, dtype) -> bool:
+    """Whether the tensor-core latent core takes this shape (bfloat16, up to 16 heads, a rank in 32s up to 256)."""
+    return LATENT_BACKEND == "mma" and dtype == torch.bfloat16 and n_heads <= 16 and rank % 32 == 0 and 32 <= rank <= 256
+
+
+def latent_core_mma(q: torch.Tensor, pages: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+                    row_entry: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, n_heads: int,
+                    window: Optional[int], scale: float) -> None:
+    """``latent_core`` for long bfloat16 steps on the tensor cores: the heads of a row are the rows of an MMA tile;
+    scores are float32 sums of exact bfloat16 products, the float32 softmax weights enter the weighted sum as three
+    bfloat16 terms each, so the sum is a float32 sum."""
+    n = q.shape[0]
+    num_pages, one, page_size, rp = pages.shape
+    if q.shape != (n, n_heads * rp) or out.shape != q.shape or one != 1 or q.dtype != torch.bfloat16 \
+            or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or (gate is not None and gate.shape != (n, n_heads)):
+        raise KernelError("latent_core_mma: shapes or dtypes do not fit")
+    _f32(gate, "gate"), _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
+    f = _fn("latent_mma", "ng_latent_core_mma", [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 6 + [_c_float, _c_void_p],
+            {"NG_LAT_RANK": rp})
+    _check(f(_ptr(q), _ptr(pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry), _ptr(gate), _ptr(out),
+             n, n_heads, rp, page_size, num_pages, int(window or 0), float(scale), _stream()), "latent_core_mma")
+
+
 def latent_core_partial_floats(n_rows: int, n_heads: int, rank: int, n_splits: int) -> int:
     return n_rows * n_heads * n_splits * (rank + 2) if n_splits > 1 else 0
 

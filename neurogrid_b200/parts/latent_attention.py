@@ -22,7 +22,8 @@ class LatentAttention:
     so the attention core is a multi-query attention in which every head reads the latent pages both as
     keys and as values: a block per row stages each tile of latents once for all heads.  Scores, softmax
     weights and their sum with the values are float32, keys are walked in ascending order, and the two
-    norms and the gate are float32 too."""
+    norms and the gate are float32 too.  Long bfloat16 steps run the core on the tensor cores with the heads
+    of a row as the rows of an MMA tile (exact products, float32 sums; the weights as three bfloat16 terms)."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
     SPLIT_MAX_ROWS = 32    # steps of up to this many rows cut each row's keys into runs
@@ -68,8 +69,12 @@ class LatentAttention:
         return PagedNeed(1, self.rank_p, self.spec.window, values=False)
 
     def kernels(self):
-        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("latent", None),
-                ("attention_generic", None)]
+        jobs = [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("latent", None)]
+        if ops.latent_core_mma_takes(self.spec.n_heads, self.rank_p, self.dtype):
+            jobs.append(("latent_mma", {"NG_LAT_RANK": self.rank_p}))
+        if not ops.latent_core_takes(self.spec.n_heads, self.rank_p):
+            jobs.append(("attention_generic", None))
+        return jobs
 
     def forward(self, x, ctx, cache):
         s = self.spec
@@ -83,7 +88,10 @@ class LatentAttention:
         q = ctx.ws.buf("lat_q", n, H * rp, self.dtype)
         ops.linear(cq, self.w_q, None, q)
         o = ctx.ws.buf("lat_o", n, H * rp, self.dtype)
-        if ops.latent_core_takes(H, rp):
+        if n > self.SPLIT_MAX_ROWS and ops.latent_core_mma_takes(H, rp, self.dtype):
+            ops.latent_core_mma(q, cache.k_pages, cache.table, ctx.positions, ctx.row_entry, gate, o, H, s.window,
+                                s.softmax_scale)
+        elif ops.latent_core_takes(H, rp):
             # a step of few rows has too few blocks for the GPU: every row's keys are cut into runs, a block each
             n_splits = 1
             if n <= self.SPLIT_MAX_ROWS:

@@ -123,7 +123,7 @@ def _run_retention(part, x, cuts, dtype, slot, state):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dk,dv,rot", [(3, 32, 20, 16), (2, 64, 64, 64), (1, 16, 136, 0), (2, 128, 128, 32),
-                                             (1, 72, 8, 72)])
+                                             (1, 72, 8, 72), (2, 16, 6, 8)])
 def test_retention_whole_cut_and_decode(dtype, heads, dk, dv, rot):
     H, T = 96, 90
     decay = [0.999, 0.9, 1.0][:heads]
@@ -234,7 +234,8 @@ def _run_latent(part, x, cuts, dtype, ps=8, pages=40, seed=0):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dk,dv,rq,rkv,window", [(3, 16, 24, 40, 20, 21), (2, 32, 32, 24, 64, None),
                                                        (5, 8, 4, 16, 100, 8), (1, 64, 16, 8, 16, 1),
-                                                       (18, 8, 8, 16, 24, 30), (33, 4, 4, 8, 250, 12), (70, 4, 4, 8, 16, 9)])
+                                                       (18, 8, 8, 16, 24, 30), (33, 4, 4, 8, 250, 12), (70, 4, 4, 8, 16, 9), (16, 8, 8, 16, 128, 40), (9, 8, 16, 24, 96, None),
+                                                       (4, 8, 8, 16, 256, 50)])
 def test_latent_attention_whole_cut_and_decode(dtype, heads, dk, dv, rq, rkv, window):
     H, T = 80, 70
     spec = LatentAttentionSpec(H, heads, dk, dv, rq, rkv, 0.4, 2e-5, window)
@@ -272,6 +273,17 @@ def test_latent_attention_window_edges(window, ps):
         assert min(rel_err(off[i], want[i]) for i in marks) > 2e-3       # twenty times what the comparison below allows
     whole = _run_latent(part, x, [(0, T)], torch.float32, ps=ps)
     assert rel_err(whole, want) < 1e-4 and max(rel_err(whole[i], want[i]) for i in marks) < 1e-4
+    # the bfloat16 path's kernels (tensor cores for the whole prompt, the split runs for single tokens): nearer to the
+    # right window than to either wrong one at the marked queries
+    part16, _, _ = _latent(spec, torch.bfloat16, seed=5, gain=1.0)
+    x16 = x.to(torch.bfloat16)
+    for got16 in (_run_latent(part16, x16, [(0, T)], torch.bfloat16, ps=ps),
+                  _run_latent(part16, x16, [(0, 2 * window)] + [(t, 1) for t in range(2 * window, T)], torch.bfloat16, ps=ps)):
+        right = max(rel_err(got16[i], want[i]) for i in marks)
+        assert right < TOL[torch.bfloat16]
+        for wrong in (window - 1, window + 1):
+            off = plain.latent_attention(xc, w, "mix.", dict(m, mask={"size": wrong}), 1e-5)
+            assert sum(rel_err(got16[i], off[i]) for i in marks) > 3 * sum(rel_err(got16[i], want[i]) for i in marks)
     head = 2 * window - 2
     at = head + window + 12                                        # decoded: 2W-2 .. 3W+9
     cuts = [(0, head)] + [(t, 1) for t in range(head, at)] + [(at + a, n) for a, n in _cuts(T - at, [2, 5, 2, 31])]
