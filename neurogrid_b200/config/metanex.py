@@ -100,8 +100,8 @@ class MetanexConfig:
                     _need(mlp["shared"], lp + "shared.", "ff", int)
         canon, side = d.get("canon"), d.get("token_side")
         taps = _need(canon, "canon.", "taps", int) if canon is not None else 0
-        if taps == 1 or taps > 8:
-            raise ConfigError(f"canon.taps = {taps} must be in [2, 8]")
+        if taps > 8:
+            raise ConfigError(f"canon.taps = {taps} must be in [1, 8]")
         cfg = cls(vocab=_need(d, "", "vocab", int), width=_need(d, "", "width", int),
                   norm_eps=_need(d.get("norm"), "norm.", "eps", float),
                   canon_taps=taps,

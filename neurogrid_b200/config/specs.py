@@ -209,8 +209,8 @@ class InputConvSpec:
     kind: str = "input_conv"
 
     def __post_init__(self):
-        if not (2 <= self.taps <= 8):
-            raise ValueError(f"input conv taps must be in [2, 8], got {self.taps}")
+        if not (1 <= self.taps <= 8):
+            raise ValueError(f"input conv taps must be in [1, 8], got {self.taps}")
 
 
 @dataclass(frozen=True)

@@ -22,10 +22,13 @@ class InputConv:
         return {"": TensorDecl((self.spec.hidden, self.spec.taps), "conv")}
 
     def bind(self, t):
-        self.weight = t[""].to(device=self.device, dtype=torch.float32).contiguous()
+        w = t[""].to(device=self.device, dtype=torch.float32)
+        if self.spec.taps == 1:              # a single tap sees the current token only: the kernel's two taps, the older one zero
+            w = torch.cat([torch.zeros_like(w), w], dim=1)
+        self.weight = w.contiguous()
 
     def cache_need(self):
-        return SlotNeed((self.spec.taps - 1, self.spec.hidden))
+        return SlotNeed((max(self.spec.taps, 2) - 1, self.spec.hidden))
 
     def kernels(self):
         return [("input_conv", None)]

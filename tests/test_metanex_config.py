@@ -58,7 +58,7 @@ def test_declared_tensors():
     (("layers", 0, "type"), "attention"), (("layers", 1, "mixer", "decay"), [0.5]),
     (("layers", 1, "mixer", "rot", "dims"), 15), (("layers", 1, "mixer", "rot", "dims"), 64),
     (("layers", 0, "mlp", "router", "top"), 6), (("layers", 0, "mixer", "kv_rank"), None),
-    (("canon", "taps"), 1), (("norm",), None), (("width",), -3), (("layers", 0, "mlp", "kind"), "dense"),
+    (("canon", "taps"), 9), (("norm",), None), (("width",), -3), (("layers", 0, "mlp", "kind"), "dense"),
 ])
 def test_bad_configurations_name_the_key(path, value):
     cfg = copy.deepcopy(mm.META_P)

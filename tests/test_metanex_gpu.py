@@ -76,7 +76,7 @@ def test_scalar_norm(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps", [2, 4, 8])
+@pytest.mark.parametrize("taps", [1, 2, 4, 8])
 def test_input_conv_whole_cut_and_slot_reuse(dtype, taps):
     H, T = 70, 75
     part = InputConv(InputConvSpec(H, taps), dtype=dtype, device=DEV)
@@ -84,7 +84,7 @@ def test_input_conv_whole_cut_and_slot_reuse(dtype, taps):
     part.bind(w)
     x = _x(T, H, dtype)
     want = plain.input_conv(x.double().cpu(), w[""].double())
-    state = torch.randn(3, taps - 1, H, device=DEV)              # stale content: a request that starts must not see it
+    state = torch.randn(3, max(taps, 2) - 1, H, device=DEV)      # stale content: a request that starts must not see it
     out = torch.empty_like(x)
     part.forward(x, make_ctx([T], [0], [1], dtype=dtype), SlotView(state), out)
     assert rel_err(out, want) < TOL[dtype]
