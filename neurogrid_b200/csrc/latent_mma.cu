@@ -1,7 +1,7 @@
 // Latent attention core for long steps (bfloat16) on the tensor cores, with float32 scores, weights and sums.
 //
 // Every head of a row reads the same latent pages as keys and as values, so the heads of ONE row are the 16
-// rows of an m16n8k16 tile: a warp takes a row, stages 32 latents at a time in shared memory (16-byte loads),
+// rows of an m16n8k16 tile: a warp takes a row, copies 32 latents at a time into shared memory (cp.async, a tile ahead),
 // and forms
 //     S[16 heads x 32 keys] = Q C^T      bfloat16 x bfloat16 products are exact, the sum is float32: float32 scores
 //     online softmax in float32 (a quad of lanes holds a head's 32 scores)
@@ -21,7 +21,7 @@ static_assert(NG_LAT_RANK % 32 == 0 && NG_LAT_RANK >= 32 && NG_LAT_RANK <= 256, 
 #define LM_R NG_LAT_RANK
 #define LM_TILE 32
 #if NG_LAT_RANK > 160
-#define LM_WARPS 2                // the warps' tiles share 48 KB of static shared memory
+#define LM_WARPS 2                // two tiles a warp (one being copied, one being used): about 70 KB a block either way
 #else
 #define LM_WARPS 4
 #endif
@@ -44,6 +44,15 @@ __device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], ui
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16 bytes global -> shared, asynchronously; `bytes` 0 writes zeros instead
+__device__ __forceinline__ void lm_cp16(bf16* dst, const bf16* src, int bytes) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lm_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void lm_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void lm_cp_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t lm_pack(float x, float y) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -63,7 +72,7 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
                        int table_stride, const int* __restrict__ positions, const int* __restrict__ row_entry,
                        const float* __restrict__ gate, bf16* __restrict__ out, int n_rows, int nH, int page_size,
                        int num_pages, int window, float scale) {
-    __shared__ __align__(16) bf16 tiles[LM_WARPS][LM_TILE * LM_LD];
+    extern __shared__ __align__(16) unsigned char lm_smem[];
     ng_pdl_trigger();
     ng_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -79,7 +88,7 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
     const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* trow = table + (size_t)entry * table_stride;
-    bf16* tile = tiles[warp];
+    bf16* bufs = reinterpret_cast<bf16*>(lm_smem) + (size_t)warp * 2 * LM_TILE * LM_LD;      // this warp's two tiles
 
     // the row's queries as A fragments: heads quad and quad + 8, all of the latent's columns
     uint32_t qa[LM_R / 16][4];
@@ -102,22 +111,37 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     constexpr int CPK = LM_R / 8;                              // 16-byte pieces of a key
-    for (int k0 = lo; k0 <= pos; k0 += LM_TILE) {
+    // a tile is copied asynchronously while the one before it is used; keys past the row's last are zero
+    auto stage = [&](int k0, bf16* dst) {
         const int n = min(LM_TILE, pos + 1 - k0);
-        __syncwarp();
-        // stage the tile: keys past the row's last are zero
 #pragma unroll
         for (int i = 0; i < CPK; ++i) {
             const int c = lane + 32 * i;
             const int k = c / CPK, part = c % CPK;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            const bf16* src = pages;
+            int bytes = 0;
             if (k < n) {
                 const int kp = k0 + k;
                 const int page = trow[kp / page_size];
-                if (page >= 0 && page < num_pages)
-                    v = *reinterpret_cast<const uint4*>(pages + ((size_t)page * page_size + (kp % page_size)) * LM_R + part * 8);
+                if (page >= 0 && page < num_pages) {
+                    src = pages + ((size_t)page * page_size + (kp % page_size)) * LM_R + part * 8;
+                    bytes = 16;
+                }
             }
-            *reinterpret_cast<uint4*>(tile + k * LM_LD + part * 8) = v;
+            lm_cp16(dst + k * LM_LD + part * 8, src, bytes);
+        }
+        lm_cp_commit();
+    };
+    stage(lo, bufs);
+    int it = 0;
+    for (int k0 = lo; k0 <= pos; k0 += LM_TILE, ++it) {
+        const int n = min(LM_TILE, pos + 1 - k0);
+        const bf16* tile = bufs + (size_t)(it & 1) * LM_TILE * LM_LD;
+        if (k0 + LM_TILE <= pos) {
+            stage(k0 + LM_TILE, bufs + (size_t)((it + 1) & 1) * LM_TILE * LM_LD);
+            lm_cp_wait_but_one();
+        } else {
+            lm_cp_wait_all();
         }
         __syncwarp();
         // scores: four tiles of 8 keys
@@ -194,6 +218,7 @@ latent_core_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ page
                 lm_mma(o[dt + 1], ph, b[2], b[3]);
             }
         }
+        __syncwarp();                                            // the tile is free for the copy after next
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -216,7 +241,14 @@ NG_EXPORT int ng_latent_core_mma(const void* q, const void* pages, const int* ta
                                  int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (rp != LM_R || nH <= 0 || nH > 16 || page_size <= 0) return NG_BAD_SIZE;
-    NG_LAUNCH((latent_core_mma_kernel), (n_rows + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, 0, stream, (const bf16*)q,
+    const size_t smem = (size_t)LM_WARPS * 2 * LM_TILE * LM_LD * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(latent_core_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        configured = true;
+    }
+    NG_LAUNCH((latent_core_mma_kernel), (n_rows + LM_WARPS - 1) / LM_WARPS, LM_WARPS * 32, smem, stream, (const bf16*)q,
               (const bf16*)pages, table, table_stride, positions, row_entry, gate, (bf16*)out, n_rows, nH, page_size, num_pages,
               window, scale);
     return ng_launch_status();
