@@ -267,8 +267,11 @@ retention_out_kernel(const T* __restrict__ x, const float* __restrict__ inv_freq
     float* Ks = Qs + RC * ldq;               // [RC][dk+1]
     float* Vs = Ks + RC * ldq;               // [RC][dvs]
     float* As = Vs + RC * dvs;               // [RC][RC+1]
-    float* Ss = As + RC * lda;               // [dk][dvs]
-    float* pw = Ss + dk * dvs;               // [RC+1]
+    float* pw = As + RC * lda;               // [RC+1]
+    // the state before the chunk, [dk][dvs]: in k's place once the scores are formed when it fits there (more blocks
+    // a SM), behind the rest otherwise
+    const bool s_over_k = dk * dvs <= RC * ldq;
+    float* Ss = s_over_k ? Ks : sm + ((2 * RC * ldq + RC * dvs + RC * lda + RC + 1 + 3) & ~3);      // 16-byte aligned
     ng_pdl_trigger();
     ng_pdl_wait();
     const int e = blockIdx.x, c = blockIdx.y, slices = dv / dvs;
@@ -288,10 +291,11 @@ retention_out_kernel(const T* __restrict__ x, const float* __restrict__ inv_freq
         Vs[idx] = t < n ? ng_ld(x + (size_t)(q0 + c * RC + t) * ld + off_v + v) : 0.f;
     }
     const float* Sb = u_scratch + (((size_t)(q0 / RC + e + c)) * nH + head) * dk * dv + v0;
-    for (int idx = tid; idx < dk * (dvs / 4); idx += RC_THREADS) {
-        const int d = idx / (dvs / 4), v4 = (idx % (dvs / 4)) * 4;
-        *reinterpret_cast<float4*>(Ss + d * dvs + v4) = *reinterpret_cast<const float4*>(Sb + (size_t)d * dv + v4);
-    }
+    if (!s_over_k)
+        for (int idx = tid; idx < dk * (dvs / 4); idx += RC_THREADS) {
+            const int d = idx / (dvs / 4), v4 = (idx % (dvs / 4)) * 4;
+            *reinterpret_cast<float4*>(Ss + d * dvs + v4) = *reinterpret_cast<const float4*>(Sb + (size_t)d * dv + v4);
+        }
     __syncthreads();
     {   // A: a 2 x 4 tile per thread (16 x 8 tiles cover RC x RC)
         const int i0 = (tid / 8) * 2, j0 = (tid % 8) * 4;
@@ -316,6 +320,13 @@ retention_out_kernel(const T* __restrict__ x, const float* __restrict__ inv_freq
             }
     }
     __syncthreads();
+    if (s_over_k) {                          // k is done with: the state takes its place
+        for (int idx = tid; idx < dk * (dvs / 4); idx += RC_THREADS) {
+            const int d = idx / (dvs / 4), v4 = (idx % (dvs / 4)) * 4;
+            *reinterpret_cast<float4*>(Ss + d * dvs + v4) = *reinterpret_cast<const float4*>(Sb + (size_t)d * dv + v4);
+        }
+        __syncthreads();
+    }
     // o: 4 x 2 tiles over RC x dvs;  inside the chunk (A V) and from the state (Q S), kept apart until the end
     for (int tile = tid; tile < (RC / 4) * (dvs / 2); tile += RC_THREADS) {
         const int i0 = (tile / (dvs / 2)) * 4, c0v = (tile % (dvs / 2)) * 2;
@@ -374,7 +385,9 @@ __global__ void retention_norm_gate_kernel(const float* __restrict__ o, const T*
 static int retention_chunk_slice(int dv) { return dv % 32 == 0 ? 32 : dv; }
 static size_t retention_out_smem(int dk, int dv) {
     const int dvs = retention_chunk_slice(dv);
-    return ((size_t)2 * RC * (dk + 1) + (size_t)RC * dvs + (size_t)RC * (RC + 1) + (size_t)dk * dvs + RC + 1) * sizeof(float);
+    const size_t base = (size_t)2 * RC * (dk + 1) + (size_t)RC * dvs + (size_t)RC * (RC + 1) + RC + 1;
+    const size_t state = (size_t)dk * dvs <= (size_t)RC * (dk + 1) ? 0 : (size_t)dk * dvs + 4;   // else it lies in k's place
+    return (base + state) * sizeof(float);
 }
 static size_t retention_local_smem(int dk, int dv) {
     return ((size_t)RC * (dk + 1) + (size_t)RC * retention_chunk_slice(dv) + RC + 1) * sizeof(float);
