@@ -102,10 +102,40 @@ __global__ void moe_swiglu_scaled_kernel(const T* __restrict__ gate_up, const fl
     ng_st(out + (size_t)row * I + c, ng_ld(&act) * w);
 }
 
+// the same, eight columns a thread with 16-byte accesses (bfloat16; I and ff multiples of 8, so that the eight share an expert)
+__global__ void moe_swiglu_scaled_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ weights,
+                                             __nv_bfloat16* __restrict__ out, int I, int E, int ff) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= I) return;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + (size_t)row * 2 * I + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + (size_t)row * 2 * I + I + c);
+    const float w = c < E * ff ? weights[(size_t)row * E + c / ff] : 1.f;
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
+    uint4 ov;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float gk = __bfloat162float(g[k]);
+        const __nv_bfloat16 act = __float2bfloat16_rn(gk / (1.f + expf(-gk)) * __bfloat162float(u[k]));
+        o[k] = __float2bfloat16_rn(__bfloat162float(act) * w);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)row * I + c) = ov;
+}
+
 NG_EXPORT int ng_moe_swiglu_scaled(const void* gate_up, const float* weights, void* out, int n_rows, int I, int E, int ff,
                                    int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (E <= 0 || ff <= 0 || I < E * ff || n_rows > 65535) return NG_BAD_SIZE;
+    if (act_bf16 && I % 8 == 0 && ff % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        dim3 vgrid((I / 8 + 127) / 128, n_rows);
+        NG_LAUNCH((moe_swiglu_scaled_vec_kernel), vgrid, 128, 0, stream, (const __nv_bfloat16*)gate_up, weights,
+                  (__nv_bfloat16*)out, I, E, ff);
+        return ng_launch_status();
+    }
     dim3 grid((I + 255) / 256, n_rows);
     if (act_bf16)
         NG_LAUNCH((moe_swiglu_scaled_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gate_up, weights,

@@ -292,9 +292,12 @@ def test_latent_attention_window_edges(window, ps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("experts,top,ff,shared", [(5, 2, 24, 40), (4, 1, 16, 0), (3, 3, 8, 16), (40, 6, 8, 8)])
-def test_moe(dtype, experts, top, ff, shared):
-    H, T = 72, 37
+@pytest.mark.parametrize("experts,top,ff,shared,T", [(5, 2, 24, 40, 37), (4, 1, 16, 0, 37), (3, 3, 8, 16, 37), (40, 6, 8, 8, 37),
+                                                      (5, 2, 24, 40, 150), (3, 2, 12, 20, 150), (6, 3, 16, 0, 2100)])
+def test_moe(dtype, experts, top, ff, shared, T):
+    """Steps of few rows (the product's fused SwiGLU, then the weights) and long ones (gate and weights in one pass,
+    eight columns a thread where the sizes allow)."""
+    H = 72
     part = build("ffn", MoESpec(H, experts, top, ff, shared), dtype=dtype, device=DEV)
     w = _mats({k: d.shape for k, d in part.tensors().items()}, 6, {"router": 3.0})
     part.bind(w)
@@ -310,7 +313,7 @@ def test_moe(dtype, experts, top, ff, shared):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,H", [(11, 88), (11, 333), (200, 88), (600, 70)])
+@pytest.mark.parametrize("rows,H", [(11, 88), (11, 333), (200, 88), (600, 70), (2100, 88)])
 def test_token_side(dtype, rows, H):
     """Few rows (the sums dealt to many blocks), and steps long enough for blocks of four and of eight rows."""
     dim, V, layer, n_layers = 6, 50, 2, 4
