@@ -28,11 +28,25 @@ from .pages import OutOfPages, OutOfSlots, PagePool, SlotPool
 class PagedNeed:
     """Keys and values per token: ``n_kv_heads * head_dim`` each; ``window`` None = keep all.
     ``values`` False: one vector per token and head only (a layer that caches a latent from which
-    it forms keys and values itself); such pages have no value half."""
+    it forms keys and values itself); such pages have no value half.  ``v_heads`` / ``v_dim``: the value half's
+    heads and size where they differ from the keys' (None: the same).  ``keep_first``: with a window, the pages
+    that hold the first that many tokens are kept as well (a mask that never loses sight of them)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    v_heads: Optional[int] = None
+    v_dim: Optional[int] = None
+    keep_first: int = 0
+
+    def value_shape(self):
+        """(heads, size) of the value half."""
+        return (self.v_heads if self.v_heads is not None else self.n_kv_heads,
+                self.v_dim if self.v_dim is not None else self.head_dim)
+
+    def elements_per_token(self) -> int:
+        vh, vd = self.value_shape()
+        return self.n_kv_heads * self.head_dim + (vh * vd if self.values else 0)
 
 
 @dataclass(frozen=True)
@@ -110,6 +124,10 @@ class CacheManager:
         first_visible = length - w + 1           # lowest key position the next query reads
         return max(0, first_visible // self.page_size)
 
+    def _kept(self, group: int) -> int:
+        """Leading pages a windowed group never gives back: those that hold the first tokens its mask keeps."""
+        return -(-self.paged_needs[group].keep_first // self.page_size)
+
     def pages_to_take(self, req_id, n_new: int) -> List[int]:
         """Per group, pages that extending the request by ``n_new`` tokens takes from the pool
         (after the pages its window has passed are given back)."""
@@ -119,7 +137,7 @@ class CacheManager:
 
     def pages_freed_first(self, req_id) -> List[int]:
         r = self._req[req_id]
-        return [max(0, min(self._passed(g, r.length), len(r.tables[g])) - r.first_live[g])
+        return [max(0, min(self._passed(g, r.length), len(r.tables[g])) - max(r.first_live[g], self._kept(g)))
                 for g in range(len(self.pools))]
 
     def can_extend(self, req_id, n_new: int) -> bool:
@@ -144,7 +162,7 @@ class CacheManager:
         for g, pool in enumerate(self.pools):
             t = r.tables[g]
             passed = min(self._passed(g, r.length), len(t))
-            for j in range(r.first_live[g], passed):
+            for j in range(max(r.first_live[g], self._kept(g)), passed):
                 pool.give_back(t[j])
                 t[j] = -1
                 self.table_rows[g][r.slot, j] = -1

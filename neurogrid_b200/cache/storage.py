@@ -66,8 +66,10 @@ class CacheStorage:
         self.v: List[torch.Tensor] = []
         for need, n_layers, pages in zip(self.paged_needs, counts_p, self.pages_per_group):
             shape = (n_layers, pages, need.n_kv_heads, page_size, need.head_dim)
+            vh, vd = need.value_shape()
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device) if need.values else None)
+            self.v.append(torch.zeros((n_layers, pages, vh, page_size, vd), dtype=dtype, device=device)
+                          if need.values else None)
         for need in self.slot_needs:
             if need.dtype not in _SLOT_DTYPES:
                 raise TypeError(f"a layer asks for state of dtype {need.dtype!r}; one of {sorted(_SLOT_DTYPES)}")
@@ -83,8 +85,7 @@ class CacheStorage:
 
     def bytes_per_token(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()
-        return sum((2 if n.values else 1) * k.shape[0] * n.n_kv_heads * n.head_dim * esz
-                   for k, n in zip(self.k, self.paged_needs))
+        return sum(k.shape[0] * n.elements_per_token() * esz for k, n in zip(self.k, self.paged_needs))
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.k + self.v + self.state if t is not None)

@@ -14,6 +14,7 @@ from typing import Any, Callable, Dict, Mapping
 
 from .lfm2 import ConfigError, Lfm2Config
 from .metanex import MetanexConfig
+from .rofulorn import RofulornConfig
 
 _ARCHITECTURES: Dict[str, Any] = {}
 _MODEL_TYPES: Dict[str, str] = {}
@@ -60,3 +61,4 @@ def load_config(model_dir: str):
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config, model_type="lfm2")
 register_architecture("Metanex", MetanexConfig)
+register_architecture("Rofulorn", RofulornConfig)

@@ -29,6 +29,16 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """y = (x - mean(x)) * rsqrt(var(x) + eps) * w, var the mean of the squared deviations; a weight and no bias.
+    ``tensor``: the weight's name relative to the norm's ("": it is stored under the norm's own name)."""
+    size: int
+    eps: float
+    tensor: str = "weight"
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
     """Rotary position encoding over the whole head.
 
@@ -37,12 +47,16 @@ class RopeSpec:
     ``rotary_dims`` (None: the whole head) rotates only the first that many coordinates of a head:
     pair i is (i, i + rotary_dims/2) or (2i, 2i+1), its angle pos * theta^(-2i/rotary_dims), and the
     rest of the head passes unchanged.
+    ``freq_scaling`` = (factor, low, high, original) rescales the frequencies by their wavelength l = 2 pi / f:
+    f stays where l < original / high, becomes f / factor where l > original / low, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
     """
     head_dim: int
     theta: float
     pairing: str = "half"
     scale: float = 1.0
     rotary_dims: Optional[int] = None
+    freq_scaling: Optional[Tuple[float, float, float, float]] = None
     kind: str = "rope"
 
     def __post_init__(self):
@@ -92,6 +106,56 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class MappedAttentionSpec:
+    """Grouped-query attention whose scores and softmax weights are float32, with ``n_maps`` score maps per head.
+
+    Query head h has ``n_maps`` queries of ``key_dim`` coordinates (rows of the q projection head by head as
+    [map 0, map 1]), KV head g as many keys and ONE value of ``value_dim``.  Per map: RMS norm of q and k over
+    key_dim (``qk_norm``; one weight each, shared by heads and maps), ``position`` on q and k,
+    s = softcap * tanh(scale * q.k / softcap) (``softcap`` None: scale * q.k), softmax over the keys j <= i with
+    i - j < ``window`` or j < ``keep_first`` (``window`` None: every j <= i).  One map: the head's output is the
+    weighted values.  Two maps: o = a_0 - lambda a_1 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` (four
+    vectors of key_dim, one lambda per layer), then o over its root mean square (``eps``, no weight) times
+    (1 - diff).  ``bias``: q, k, v and the output projection have biases.
+    ``cache_window`` / ``cache_keep_first``: what the layer's pages must keep: its own mask, or the widest mask among
+    the layers that read its keys and values.
+    """
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    position: object
+    softmax_scale: float
+    n_maps: int = 1
+    qk_norm: bool = False
+    eps: float = 1e-6
+    window: Optional[int] = None
+    keep_first: int = 0
+    softcap: Optional[float] = None
+    diff: float = 0.0
+    bias: bool = False
+    cache_window: Optional[int] = None
+    cache_keep_first: int = 0
+    names: Mapping[str, str] = field(default_factory=lambda: _names(
+        q="q", k="k", v="v", o="o", q_bias="q.b", k_bias="k.b", v_bias="v.b", o_bias="o.b", q_norm="q.norm",
+        k_norm="k.norm", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2"))
+    kind: str = "mapped_attention"
+
+    def __post_init__(self):
+        if self.n_maps not in (1, 2):
+            raise ValueError(f"mapped attention has one or two maps per head, got {self.n_maps}")
+        if self.n_heads < 1 or self.n_kv_heads < 1 or self.n_heads % self.n_kv_heads:
+            raise ValueError(f"n_heads {self.n_heads} is not a multiple of n_kv_heads {self.n_kv_heads}")
+        if not (1 <= self.key_dim <= 512) or not (1 <= self.value_dim <= 256):
+            raise ValueError(f"mapped attention: key_dim in [1, 512] and value_dim in [1, 256], got {self.key_dim}, {self.value_dim}")
+        if self.window is not None and self.window < 1:
+            raise ValueError("attention window must be >= 1")
+        if self.keep_first < 0 or (self.softcap is not None and not self.softcap > 0):
+            raise ValueError("keep_first must be >= 0 and softcap positive")
+
+
+@dataclass(frozen=True)
 class ShortConvSpec:
     """Gated causal depthwise convolution of width ``width`` (state: last width-1 inputs)."""
     hidden: int
@@ -108,12 +172,19 @@ class ShortConvSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """down( silu(gate(x)) * up(x) ), no biases."""
+    """down( act(gate(x)) * up(x) ), no biases; ``activation`` "silu" or "gelu_tanh" (the tanh form of gelu).
+    A tensor's name is its role's name plus ``weight_suffix``."""
     hidden: int
     intermediate: int
     names: Mapping[str, str] = field(default_factory=lambda: _names(
         gate="gate_proj", up="up_proj", down="down_proj"))
+    activation: str = "silu"
+    weight_suffix: str = ".weight"
     kind: str = "swiglu"
+
+    def __post_init__(self):
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation must be silu or gelu_tanh, got {self.activation!r}")
 
 
 @dataclass(frozen=True)
@@ -274,6 +345,7 @@ class ModelSpec:
     final_norm_name: str = "model.norm.weight"
     head_name: str = "lm_head.weight"
     eos_token_ids: Tuple[int, ...] = ()
+    embed_scale: float = 1.0                     # the token embeddings are multiplied by this
     position_table_name: Optional[str] = None    # a table [max_positions, hidden] of learned positions, added to the
                                                  # token embeddings (no LFM2 configuration has one)
 

@@ -36,6 +36,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "gemm_sm100": (),
     "attention_sm100": (),
     "input_conv": (), "retention": (), "latent": (), "latent_mma": (), "moe": (), "token_side": (),
+    "mapped_attention": (),
 }
 
 _lock = threading.RLock()

@@ -11,7 +11,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int H, int V, int* __restrict__ status, int accumulate,
-                             int bad_bit) {
+                             int bad_bit, float scale) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.x;
@@ -24,7 +24,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const T* src = table + (size_t)tok * H;
     float* dst = out + (size_t)row * H;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        const float v = bad ? 0.f : ng_ld(src + j);
+        const float v = bad ? 0.f : ng_ld(src + j) * scale;
         dst[j] = accumulate ? dst[j] + v : v;
     }
 }
@@ -32,17 +32,18 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // out[row] = table[index[row]], or out[row] += ... when `accumulate` (a table of learned positions
 // added to the token embeddings: the index is then the row's position).  An index outside the
 // table gives zeros and sets `bad_bit` in the status word.
+// Every looked-up row is multiplied by `scale` (1 for most models) in float32.
 NG_EXPORT int ng_embed(const void* table, int table_bf16, const int* tokens, float* out, int n_rows,
-                       int H, int V, int* status, int accumulate, int bad_bit, cudaStream_t stream) {
+                       int H, int V, int* status, int accumulate, int bad_bit, float scale, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (H <= 0 || V <= 0) return NG_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_bf16)
         NG_LAUNCH((embed_kernel<__nv_bfloat16>), n_rows, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, H, V,
-                  status, accumulate, bad_bit);
+                  status, accumulate, bad_bit, scale);
     else
         NG_LAUNCH((embed_kernel<float>), n_rows, threads, 0, stream, (const float*)table, tokens, out, H, V, status,
-                  accumulate, bad_bit);
+                  accumulate, bad_bit, scale);
     return ng_launch_status();
 }
 
@@ -192,6 +193,84 @@ NG_EXPORT int ng_add_rmsnorm(float* h, const void* delta, const float* w, void* 
     return ng_launch_status();
 }
 
+// ---------------------------------------------------------------------------------- add + layernorm
+// One block per output row i, src row = rows ? rows[i] : i:
+//   h[src] += delta[src] (float32 sum, written back; delta as for add_rmsnorm)
+//   out[i] = (h[src] - mean) * rsqrt(var + eps) * w,   var = mean of the squared deviations; no bias
+//   h[src] += post[.] afterwards if `post` is given: a vector that belongs to the sum the layer adds to the
+//   stream later (the bias of a product whose epilogue adds straight into the stream)
+// Each thread keeps its NV elements of the row in registers: the row is read once.
+template <typename TD, typename TO, int NV>
+__global__ void add_layernorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ w,
+                                     TO* __restrict__ out, const int* __restrict__ rows, const float* __restrict__ post,
+                                     int H, float eps, int n_partials, size_t partial_stride) {
+    __shared__ float red[32];
+    ng_pdl_trigger();
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    float* hr = h + (size_t)src * H;
+    float v[NV];
+    ng_pdl_wait();
+    delta = ng_after_wait(delta);
+    float sum = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = threadIdx.x + u * blockDim.x;
+        v[u] = 0.f;
+        if (j < H) {
+            v[u] = hr[j];
+            if (delta)
+                for (int s = 0; s < n_partials; ++s) v[u] += ng_ld(delta + s * partial_stride + (size_t)src * H + j);
+            sum += v[u];
+        }
+    }
+    const float mean = ng_block_sum(sum, red) / (float)H;
+    float sq = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = threadIdx.x + u * blockDim.x;
+        if (j < H) sq += (v[u] - mean) * (v[u] - mean);
+    }
+    const float r = rsqrtf(ng_block_sum(sq, red) / (float)H + eps);
+    TO* orow = out + (size_t)i * H;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = threadIdx.x + u * blockDim.x;
+        if (j < H) {
+            ng_st(orow + j, (v[u] - mean) * r * w[j]);
+            if (delta || post) hr[j] = v[u] + (post ? post[j] : 0.f);
+        }
+    }
+}
+
+template <typename TD, typename TO>
+static int launch_add_layernorm(float* h, const void* delta, const float* w, void* out, const int* rows, const float* post,
+                                int n_out, int H, float eps, int n_partials, size_t ps, cudaStream_t stream) {
+    const int threads = H <= 1024 ? 128 : H <= 4096 ? 256 : 1024;
+    const int nv = (H + threads - 1) / threads;
+#define LN_GO(NV) NG_LAUNCH((add_layernorm_kernel<TD, TO, NV>), n_out, threads, 0, stream, h, (const TD*)delta, w, (TO*)out, \
+                            rows, post, H, eps, n_partials, ps)
+    if (nv <= 2) LN_GO(2);
+    else if (nv <= 4) LN_GO(4);
+    else if (nv <= 8) LN_GO(8);
+    else if (nv <= 16) LN_GO(16);
+    else return NG_BAD_SIZE;
+#undef LN_GO
+    return ng_launch_status();
+}
+
+// `rows` and `post` do not go together with a delta on gathered rows: a gathered row may be named twice.
+NG_EXPORT int ng_add_layernorm(float* h, const void* delta, const float* w, void* out, const int* rows, const float* post,
+                               int n_out, int H, float eps, int act_bf16, int delta_f32, int n_partials,
+                               long long partial_stride, cudaStream_t stream) {
+    if (n_out <= 0) return NG_OK;
+    if (H <= 0 || n_partials < 1 || (rows && post)) return NG_BAD_SIZE;
+    const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && delta_f32) return launch_add_layernorm<float, __nv_bfloat16>(h, delta, w, out, rows, post, n_out, H, eps, n_partials, ps, stream);
+    if (act_bf16) return launch_add_layernorm<__nv_bfloat16, __nv_bfloat16>(h, delta, w, out, rows, post, n_out, H, eps, 1, 0, stream);
+    return launch_add_layernorm<float, float>(h, delta, w, out, rows, post, n_out, H, eps, delta_f32 ? n_partials : 1, ps, stream);
+}
+
 // h[row] += delta[row] only (the last residual sum of a model whose output is not normed here)
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n, int n_partials) {
@@ -214,9 +293,15 @@ NG_EXPORT int ng_residual_add(float* h, const void* delta, long long n, int delt
 }
 
 // ---------------------------------------------------------------------------------- swiglu
-// gu is [n_rows, 2*I]: gate = gu[:, :I], up = gu[:, I:];  out = silu(gate) * up, float32 math.
+// gu is [n_rows, 2*I]: gate = gu[:, :I], up = gu[:, I:];  out = act(gate) * up, float32 math;
+// act: silu, or (`gelu`) the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  `out` rows lie
+// `ldo` elements apart (a column block of a wider buffer).
+__device__ __forceinline__ float ng_gate_act(float g, int gelu) {
+    if (gelu) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.f + expf(-g));
+}
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int ldo, int gelu) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const size_t row = blockIdx.x;
@@ -224,12 +309,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     if (j >= I) return;
     const float g = ng_ld(gu + row * 2 * (size_t)I + j);
     const float u = ng_ld(gu + row * 2 * (size_t)I + I + j);
-    const float s = g / (1.f + expf(-g));
-    ng_st(out + row * (size_t)I + j, s * u);
+    ng_st(out + row * (size_t)ldo + j, ng_gate_act(g, gelu) * u);
 }
 
 // bfloat16, I % 8 == 0: eight elements (16 bytes of gate, 16 of up) per thread
-__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, int ldo,
+                                     int gelu) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const size_t row = blockIdx.x;
@@ -245,21 +330,21 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
     for (int k = 0; k < 4; ++k) {
         const float ga = __low2float(g2[k]), gb = __high2float(g2[k]);
         const float ua = __low2float(u2[k]), ub = __high2float(u2[k]);
-        o2[k] = __floats2bfloat162_rn(ga / (1.f + expf(-ga)) * ua, gb / (1.f + expf(-gb)) * ub);
+        o2[k] = __floats2bfloat162_rn(ng_gate_act(ga, gelu) * ua, ng_gate_act(gb, gelu) * ub);
     }
-    *reinterpret_cast<uint4*>(out + row * (size_t)I + j) = o4;
+    *reinterpret_cast<uint4*>(out + row * (size_t)ldo + j) = o4;
 }
 
-NG_EXPORT int ng_swiglu(const void* gu, void* out, int n_rows, int I, int act_bf16, cudaStream_t stream) {
+NG_EXPORT int ng_swiglu(const void* gu, void* out, int n_rows, int I, int ldo, int gelu, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (I <= 0 || (I + 255) / 256 > 65535) return NG_BAD_SIZE;
-    if (act_bf16 && I % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    if (I <= 0 || (I + 255) / 256 > 65535 || ldo < I) return NG_BAD_SIZE;
+    if (act_bf16 && I % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         dim3 grid8(n_rows, (I / 8 + 127) / 128);
-        NG_LAUNCH((swiglu_bf16x8_kernel), grid8, 128, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+        NG_LAUNCH((swiglu_bf16x8_kernel), grid8, 128, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, ldo, gelu);
         return ng_launch_status();
     }
     dim3 grid(n_rows, (I + 255) / 256);
-    if (act_bf16) NG_LAUNCH((swiglu_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
-    else NG_LAUNCH((swiglu_kernel<float>), grid, 256, 0, stream, (const float*)gu, (float*)out, I);
+    if (act_bf16) NG_LAUNCH((swiglu_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, ldo, gelu);
+    else NG_LAUNCH((swiglu_kernel<float>), grid, 256, 0, stream, (const float*)gu, (float*)out, I, ldo, gelu);
     return ng_launch_status();
 }

@@ -93,17 +93,17 @@ def _fn(lib_name: str, symbol: str, argtypes, defines=None):
 
 # ----------------------------------------------------------------------------- elementwise
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-          accumulate: bool = False) -> None:
-    """out[N,H] (float32) = table[tokens]; a token outside the table gives zeros and a status bit.
+          accumulate: bool = False, scale: float = 1.0) -> None:
+    """out[N,H] (float32) = table[tokens] * scale; a token outside the table gives zeros and a status bit.
     ``accumulate``: out += table[tokens] instead (``tokens`` are then positions into a table of
     learned positions; one outside the table sets the bad-position bit)."""
     n, H = out.shape
     V = table.shape[0]
     f = _fn("elementwise", "ng_embed", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                                       _c_void_p, _c_int, _c_int, _c_void_p])
+                                       _c_void_p, _c_int, _c_int, _c_float, _c_void_p])
     _f32(out, "embed out"), _i32(tokens, "tokens"), _i32(status, "status")
     _check(f(_ptr(table, "embedding table"), _act_flag(table, "embedding table"), _ptr(tokens), _ptr(out),
-             n, H, V, _ptr(status), int(accumulate), 4 if accumulate else 1, _stream()), "embed")
+             n, H, V, _ptr(status), int(accumulate), 4 if accumulate else 1, float(scale), _stream()), "embed")
 
 
 def _partials(delta: Optional[torch.Tensor], h: torch.Tensor, act: int):
@@ -141,6 +141,21 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
              stride, _stream()), "add_rmsnorm")
 
 
+def add_layernorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                  eps: float, rows: Optional[torch.Tensor] = None, post: Optional[torch.Tensor] = None) -> None:
+    """h[N,H] float32 (+= delta if given, as for ``add_rmsnorm``); out[i] = (x - mean(x)) * rsqrt(var(x) + eps) * weight
+    for x = h[rows[i] if rows else i], var the mean of the squared deviations, no bias.  ``post`` (float32 [H]) is
+    added to h after the norm has read it: a vector that belongs to what the layer adds to the stream later."""
+    n_out, H = out.shape
+    act = _act_flag(out, "norm out")
+    _f32(h, "residual stream"), _f32(weight, "norm weight"), _i32(rows, "rows"), _f32(post, "post")
+    d32, n_part, stride = _partials(delta, h, act)
+    f = _fn("elementwise", "ng_add_layernorm", [_c_void_p] * 6 + [_c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ll,
+                                               _c_void_p])
+    _check(f(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), _ptr(post), n_out, H, float(eps), act, d32, n_part,
+             stride, _stream()), "add_layernorm")
+
+
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
     """h (float32) += delta (or the sum of a float32 stack [S,N,H])."""
     _f32(h, "residual stream")
@@ -149,13 +164,26 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
     _check(f(_ptr(h), _ptr(delta), h.numel(), int(delta.dtype == torch.bfloat16), n_part, _stream()), "residual_add")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[N,I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+GATE_ACTIVATIONS = ("silu", "gelu_tanh")
+
+
+def _column_block(out: torch.Tensor, what: str) -> int:
+    """Row pitch of ``out`` [N, I], which may be a block of columns of a wider row-major buffer."""
+    if out.dim() != 2 or out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError(f"{what} must be a CUDA matrix, or a block of columns of one")
+    return out.stride(0) if out.shape[0] > 1 else max(out.stride(0), out.shape[1])
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[N,I] = act(gate_up[:, :I]) * gate_up[:, I:], act = silu or the tanh form of gelu.  ``out`` may be a block
+    of columns of a wider buffer."""
     n, I = out.shape
-    if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype:
+    if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype or activation not in GATE_ACTIVATIONS:
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
-    f = _fn("elementwise", "ng_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
-    _check(f(_ptr(gate_up), _ptr(out), n, I, _act_flag(out, "swiglu out"), _stream()), "swiglu")
+    ldo = _column_block(out, "swiglu out")
+    f = _fn("elementwise", "ng_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(gate_up), out.data_ptr(), n, I, ldo, int(activation == "gelu_tanh"), _act_flag(out, "swiglu out"),
+             _stream()), "swiglu")
 
 
 # ----------------------------------------------------------------------------- float32 product
@@ -356,6 +384,71 @@ def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              _ptr(out), _ptr(scratch), n_entries, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
              float(scale), int(n_splits), int(max_ctx), _slopes(slopes, n_heads), _stream()), "attn_decode_bf16")
+
+
+# ----------------------------------------------------------------------------- attention with float32 weights
+def qkv_prep(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+             inv_freq: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+             table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor, n_q: int, n_k: int, n_v: int,
+             dim: int, vdim: int, eps: float, status: torch.Tensor) -> None:
+    """qkv[N, (n_q + n_k) * dim + n_v * vdim]: every q and k head (a map of a head counts as one) gets its RMS norm
+    over ``dim`` (if its weight is given; float32, shared by all heads) and the rotation of its first
+    2 * len(inv_freq) coordinates in pairs (2i, 2i+1) by position * inv_freq[i]; q -> q_out[N, n_q * dim],
+    k -> k_pages[P, n_k, page, dim], v -> v_pages[P, n_v, page, vdim].  n_k = n_v = 0 (no pages): a layer that
+    reads another layer's keys and values."""
+    n = q_out.shape[0]
+    if q_out.shape != (n, n_q * dim) or qkv.shape != (n, (n_q + n_k) * dim + n_v * vdim) or qkv.dtype != q_out.dtype:
+        raise KernelError("qkv_prep: shapes or dtypes do not fit")
+    page_size = num_pages = 1
+    if n_k or n_v:
+        if k_pages.dtype != q_out.dtype or v_pages.dtype != q_out.dtype or k_pages.shape[1:] != (n_k, k_pages.shape[2], dim) \
+                or v_pages.shape != (k_pages.shape[0], n_v, k_pages.shape[2], vdim):
+            raise KernelError("qkv_prep: pages do not fit the projection")
+        num_pages, page_size = k_pages.shape[0], k_pages.shape[2]
+    _f32(q_weight, "q norm weight"), _f32(k_weight, "k norm weight"), _f32(inv_freq, "inv_freq")
+    _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
+    rot_dims = 2 * inv_freq.numel() if inv_freq is not None else 0
+    f = _fn("mapped_attention", "ng_qkv_prep", [_c_void_p] * 5 + [_c_int] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2
+            + [_c_int] * 8 + [_c_float, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), rot_dims,
+             _ptr(k_pages) if n_k else None, _ptr(v_pages) if n_v else None, _ptr(table), table.shape[1], _ptr(positions),
+             _ptr(row_entry), n, n_q, n_k, n_v, dim, vdim, page_size, num_pages, float(eps), _ptr(status),
+             _act_flag(q_out, "q_out"), _stream()), "qkv_prep")
+
+
+def mapped_attention_partial_floats(n_rows: int, n_heads: int, n_maps: int, vdim: int, n_splits: int) -> int:
+    return n_rows * n_heads * n_splits * n_maps * (vdim + 2) if n_splits > 1 else 0
+
+
+def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                     positions: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor, n_heads: int, n_maps: int,
+                     window: Optional[int], keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool,
+                     post_scale: float, eps: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+    """Attention with float32 scores and weights over keys [P, G * n_maps, page, dim] and values [P, G, page, vdim]:
+    per head and map m, a_m = softmax(cap(scale * q_m . k_m)) v over the keys j <= pos with pos - j < window or
+    j < keep_first (window None: all), cap(s) = softcap * tanh(s / softcap) (softcap 0: none); the head's output is
+    a_0 (one map) or a_0 - lam * a_1 (two), then, with ``head_norm``, over its root mean square (eps) times
+    ``post_scale``.  ``out`` [N, n_heads * vdim] may be a block of columns of a wider buffer.  ``n_splits`` > 1 cuts
+    every row's keys into runs, a block each, merged through ``partial`` (float32,
+    ``mapped_attention_partial_floats`` values): for steps of few rows."""
+    n = q.shape[0]
+    num_pages, n_k, page_size, dim = k_pages.shape
+    n_g, vdim = v_pages.shape[1], v_pages.shape[3]
+    if n_k != n_g * n_maps or q.shape != (n, n_heads * n_maps * dim) or out.shape != (n, n_heads * vdim) \
+            or q.dtype != k_pages.dtype or out.dtype != q.dtype or v_pages.dtype != q.dtype \
+            or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+        raise KernelError("mapped_attention: shapes or dtypes do not fit")
+    _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _f32(partial, "partial")
+    need = mapped_attention_partial_floats(n, n_heads, n_maps, vdim, n_splits)
+    if need and (partial is None or partial.numel() < need):
+        raise KernelError(f"mapped_attention: the runs need {need} float32 values")
+    f = _fn("mapped_attention", "ng_mapped_attention", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int, _c_void_p]
+            + [_c_int] * 11 + [_c_float] * 5 + [_c_int, _c_int, _c_void_p])
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions), _ptr(row_entry),
+             out.data_ptr(), _column_block(out, "attention out"), _ptr(partial) if need else None, n, n_heads, n_g, n_maps,
+             dim, vdim, page_size, num_pages, int(window or 0), int(keep_first), int(n_splits), float(scale),
+             float(softcap or 0.0), float(lam), float(post_scale), float(eps), int(bool(head_norm)),
+             _act_flag(q, "q"), _stream()), "mapped_attention")
 
 
 # ----------------------------------------------------------------------------- input convolution
@@ -663,17 +756,20 @@ def gemm_splits(K: int, splits: int) -> int:
     return -(-total // per)
 
 
-def gemm_swiglu_sm100(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
-    """out[M,I] = silu(x wg^T) * (x wu^T) with w_gate_up = [wg (I rows); wu (I rows)]: the gate is
-    applied in the product's epilogue."""
+def gemm_swiglu_sm100(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0,
+                      activation: str = "silu") -> None:
+    """out[M,I] = act(x wg^T) * (x wu^T) with w_gate_up = [wg (I rows); wu (I rows)]: the gate is
+    applied in the product's epilogue (act = silu or the tanh form of gelu).  ``out`` may be a block of columns
+    of a wider buffer."""
     M, K = x.shape
     I = out.shape[1]
-    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
+    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16 or activation not in GATE_ACTIVATIONS:
         raise KernelError("gemm_swiglu_sm100: shapes do not fit")
+    ldc = _column_block(out, "gemm_swiglu_sm100 out")
     status = _ptr(_gemm_status(w_gate_up.device))
     f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
-    _check(f(_ptr(x), _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, token_tile, status, _stream()),
-           "gemm_swiglu_sm100")
+    _check(f(_ptr(x), _ptr(w_gate_up), None, out.data_ptr(), M, I, K, 2 * I, ldc, 4 if activation == "gelu_tanh" else 2, 1, I,
+             token_tile, status, _stream()), "gemm_swiglu_sm100")
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -721,6 +817,11 @@ def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     out = ws.buf(name, M, N, x.dtype)
     linear(x, weight, bias, out)
     return out
+
+
+def residual_add_fusable(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear_to_residual(x, weight, None, ..., residual=h)`` adds the product into ``h`` itself."""
+    return FUSE_RED and x.shape[0] <= min(64, FUSE_MAX_ROWS) and gemm_sm100_ok(x, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

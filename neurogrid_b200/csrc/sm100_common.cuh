@@ -119,6 +119,11 @@ __device__ __forceinline__ float silu_fast(float g) {
     return __fdividef(g, 1.f + e);
 }
 
+// the tanh form of gelu, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); the result is rounded to bfloat16 by its user
+__device__ __forceinline__ float gelu_tanh(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16), written
 // by TMA with the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_desc_sw128(const void* smem_tile) {

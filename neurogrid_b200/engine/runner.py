@@ -120,8 +120,7 @@ class ModelRunner:
         from ..cache.manager import PagedNeed
         esz = torch.empty((), dtype=model.dtype).element_size()
         flat = [n for need in model.cache_needs().values() for n in (need if isinstance(need, tuple) else (need,))]
-        return sum((2 if n.values else 1) * n.n_kv_heads * n.head_dim * page_size * esz
-                   for n in flat if isinstance(n, PagedNeed))
+        return sum(n.elements_per_token() * page_size * esz for n in flat if isinstance(n, PagedNeed))
 
     # ------------------------------------------------------------------ requests
     def admit(self, req_id: Hashable) -> int:

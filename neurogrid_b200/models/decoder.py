@@ -137,7 +137,7 @@ class Decoder:
         """The float32 residual stream [N, H] holding the embeddings of the step's tokens."""
         s = self.spec
         h = ctx.ws.buf("residual", ctx.n_rows, s.hidden, torch.float32)
-        ops.embed(self.embed_table, ctx.tokens, h, ctx.status)
+        ops.embed(self.embed_table, ctx.tokens, h, ctx.status, scale=s.embed_scale)
         if self.position_table is not None:                  # learned absolute positions: h += table[position]
             ops.embed(self.position_table, ctx.positions, h, ctx.status, accumulate=True)
         return h

@@ -150,3 +150,93 @@ class PreNormConvSideBlock:
             ops.residual_add(h, out)              # the token input reads the complete stream
         self.side.forward(h, ctx)
         return None
+
+
+@register("block", "parallel")
+class ParallelBlock:
+    """One norm, both sublayers read it:  u = norm(x);  x += mixer(u) + ffn(u).
+
+    When the mixer and the feed-forward both offer their inner activations (``inner_width()``, ``out_weight()`` and
+    ``core`` / ``gated``), the two output projections are ONE product: the activations lie side by side in one buffer
+    and the two matrices side by side along the contraction (stacked when bound), so the layer adds to the stream
+    once.  In a step of few rows that product adds straight into the float32 stream; a bias of the mixer's
+    projection is then added by the norm kernel, after it has read the stream.  Otherwise the sublayers run one
+    after the other.  ``spec.ffn`` None: the layer has no feed-forward."""
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        kw = dict(dtype=dtype, device=device)
+        mixer_kw = dict(kw)
+        if not owns_cache:
+            mixer_kw["owns_cache"] = False
+        self.mixer = registry.build("mixer", spec.mixer, **mixer_kw)
+        self.ffn = registry.build("ffn", spec.ffn, **kw) if spec.ffn is not None else None
+        self.norm = registry.build("norm", spec.mixer_norm, **kw)
+        self.joint = all(hasattr(self.mixer, a) for a in ("inner_width", "out_weight", "core")) and \
+            (self.ffn is None or all(hasattr(self.ffn, a) for a in ("inner_width", "out_weight", "gated")))
+        self.w_out = self.b_out = self.b_out_f32 = None
+
+    def parts(self):
+        n = self.spec.names
+        roles = {"mixer": self.mixer, "ffn": self.ffn, "mixer_norm": self.norm}
+        return {n[r]: p for r, p in roles.items() if p is not None}
+
+    def tensors(self):
+        out = {}
+        for sub, part in self.parts().items():
+            for name, decl in part.tensors().items():
+                out[f"{sub}.{name}" if name else sub] = decl
+        return out
+
+    def bind(self, t):
+        import torch
+        for sub, part in self.parts().items():
+            pre = sub + "."
+            own = {k[len(pre):]: v for k, v in t.items() if k.startswith(pre)}
+            if sub in t:
+                own[""] = t[sub]
+            part.bind(own)
+        if self.joint:
+            w, b = self.mixer.out_weight()
+            if self.ffn is not None:
+                w2, b2 = self.ffn.out_weight()
+                w = torch.cat([w, w2], dim=1).contiguous()
+                b = b if b2 is None else (b2 if b is None else b + b2)
+            self.w_out, self.b_out = w, b
+            self.b_out_f32 = b.to(torch.float32).contiguous() if b is not None else None
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def kernels(self):
+        return [job for p in self.parts().values() for job in getattr(p, "kernels", list)()]
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in self.parts().values())
+
+    def forward(self, h, pending, ctx, cache):
+        from ..csrc import ops
+        n, H = h.shape
+        buf = ctx.ws.buf("normed", n, H, self.dtype)
+        if not self.joint:
+            ctx.residual = h if ctx.fuse_residual else None
+            x = self.norm.forward(h, pending, buf)
+            m = self.mixer.forward(x, ctx, cache)
+            if m is not None:
+                ops.residual_add(h, m)
+            return self.ffn.forward(x, ctx) if self.ffn is not None else None
+        ka = self.mixer.inner_width()
+        inner = ctx.ws.buf("parallel_inner", n, self.w_out.shape[1], self.dtype)
+        fused = ctx.fuse_residual and ops.residual_add_fusable(inner, self.w_out) and \
+            (self.b_out is None or getattr(self.norm, "takes_post", False))
+        if fused and self.b_out is not None:
+            x = self.norm.forward(h, pending, buf, post=self.b_out_f32)
+        else:
+            x = self.norm.forward(h, pending, buf)
+        self.mixer.core(x, ctx, cache, inner[:, :ka])
+        if self.ffn is not None:
+            self.ffn.gated(x, ctx, inner[:, ka:])
+        if fused:
+            return ops.linear_to_residual(inner, self.w_out, None, ctx.ws, "parallel_out", residual=h)
+        return ops.linear_to_residual(inner, self.w_out, self.b_out, ctx.ws, "parallel_out")

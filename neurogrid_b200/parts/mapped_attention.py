@@ -1,0 +1,145 @@
+"""Attention with float32 scores and weights, one or two score maps per head, a window that keeps the first tokens."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.manager import PagedNeed
+from ..csrc import ops
+from ..weights.decl import TensorDecl
+from . import registry
+from .base import PositionArgs
+from .registry import register
+
+
+@register("mixer", "mapped_attention")
+class MappedAttention:
+    """q, k, v projections (stacked into one product when bound, biases added there) -> per-map RMS norm of q and
+    k -> rotation -> k, v into the layer's pages -> per head and map softmax(cap(scale q.k)) v over the visible
+    keys -> one map: that; two maps: a_0 - lambda a_1, over its root mean square, times (1 - diff) -> output
+    projection.  Keys lie in the pages as G * n_maps heads of key_dim, values as G heads of value_dim.  Scores,
+    softmax weights, their sums with the values, norms, angles and lambda are float32 in both compute dtypes.
+
+    ``owns_cache`` False builds a layer that reads another layer's keys and values: it has no k/v tensors.
+    Steps of few rows cut every row's keys into runs (a block each) so that the GPU is filled.
+    """
+
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+    SPLIT_MAX_ROWS = 32    # steps of up to this many rows may cut each row's keys into runs
+    SPLIT_MIN_KEYS = 256   # ... of at least this many keys
+    MAX_SPLITS = 16
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
+        self.position = registry.build("position", spec.position, device=device)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+        self.lam = 0.0
+
+    def _proj(self):
+        s = self.spec
+        rows = {"q": s.n_heads * s.n_maps * s.key_dim, "k": s.n_kv_heads * s.n_maps * s.key_dim,
+                "v": s.n_kv_heads * s.value_dim}
+        return {p: rows[p] for p in (("q", "k", "v") if self.owns_cache else ("q",))}
+
+    def tensors(self):
+        s, n = self.spec, self.spec.names
+        d = {n[p]: TensorDecl((rows, s.hidden)) for p, rows in self._proj().items()}
+        d[n["o"]] = TensorDecl((s.hidden, s.n_heads * s.value_dim))
+        if s.bias:
+            for p, rows in self._proj().items():
+                d[n[p + "_bias"]] = TensorDecl((rows,), "bias")
+            d[n["o_bias"]] = TensorDecl((s.hidden,), "bias")
+        if s.qk_norm:
+            d[n["q_norm"]] = TensorDecl((s.key_dim,), "norm")
+            if self.owns_cache:
+                d[n["k_norm"]] = TensorDecl((s.key_dim,), "norm")
+        if s.n_maps == 2:
+            for v in ("lq1", "lk1", "lq2", "lk2"):
+                d[n[v]] = TensorDecl((s.key_dim,), "bias")
+        return d
+
+    def bind(self, t):
+        s, n = self.spec, self.spec.names
+        kw = dict(device=self.device, dtype=self.dtype)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        self.w_qkv = torch.cat([t[n[p]].to(**kw) for p in self._proj()]).contiguous()
+        self.w_o = t[n["o"]].to(**kw).contiguous()
+        if s.bias:
+            self.b_qkv = torch.cat([t[n[p + "_bias"]].to(**kw) for p in self._proj()]).contiguous()
+            self.b_o = t[n["o_bias"]].to(**kw).contiguous()
+        if s.qk_norm:
+            self.q_norm = t[n["q_norm"]].to(**f32).contiguous()
+            if self.owns_cache:
+                self.k_norm = t[n["k_norm"]].to(**f32).contiguous()
+        if s.n_maps == 2:            # one number per layer, formed in float32 as the stored vectors' products
+            v = {k: t[n[k]].to(torch.float32) for k in ("lq1", "lk1", "lq2", "lk2")}
+            self.lam = float(torch.exp((v["lq1"] * v["lk1"]).sum()) - torch.exp((v["lq2"] * v["lk2"]).sum())) + float(s.diff)
+
+    def cache_need(self):
+        s = self.spec
+        return PagedNeed(s.n_kv_heads * s.n_maps, s.key_dim, s.cache_window, True, v_heads=s.n_kv_heads, v_dim=s.value_dim,
+                         keep_first=s.cache_keep_first if s.cache_window else 0)
+
+    def kernels(self):
+        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("mapped_attention", None)]
+
+    def scratch_bytes_per_row(self):
+        s = self.spec
+        return 4 * ops.mapped_attention_partial_floats(1, s.n_heads, s.n_maps, s.value_dim, self.MAX_SPLITS)
+
+    # a block arrangement that ends mixer and feed-forward with ONE product calls ``core`` and multiplies itself
+    def inner_width(self):
+        return self.spec.n_heads * self.spec.value_dim
+
+    def out_weight(self):
+        return self.w_o, self.b_o
+
+    def _splits(self, n_rows, cache):
+        """Runs a row's keys are cut into: from the step's rows and the layer's constants only (a graph's launches)."""
+        s = self.spec
+        if n_rows > self.SPLIT_MAX_ROWS:
+            return 1
+        longest = cache.table.shape[1] * cache.k_pages.shape[2]
+        if s.window:
+            longest = min(longest, s.window + s.keep_first)
+        want = -(-2 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))
+        return max(1, min(self.MAX_SPLITS, want, longest // self.SPLIT_MIN_KEYS))
+
+    def core(self, x, ctx, cache, out):
+        """out[N, n_heads * value_dim] (may be a block of columns of a wider buffer): the heads' outputs."""
+        s = self.spec
+        n = x.shape[0]
+        if cache.writes and not self.owns_cache:
+            raise RuntimeError("an attention layer without k/v weights cannot write a cache")
+        writes = cache.writes
+        n_q = s.n_heads * s.n_maps
+        n_k, n_v = (s.n_kv_heads * s.n_maps, s.n_kv_heads) if self.owns_cache else (0, 0)
+        qkv = ctx.ws.buf("mattn_qkv", n, self.w_qkv.shape[0], self.dtype)
+        ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        if self.owns_cache and not writes:       # has k/v weights but this run reads another cache: the q columns only
+            q_only = ctx.ws.buf("mattn_qonly", n, n_q * s.key_dim, self.dtype)
+            q_only.copy_(qkv[:, : n_q * s.key_dim])
+            qkv, n_k, n_v = q_only, 0, 0
+        q = ctx.ws.buf("mattn_q", n, n_q * s.key_dim, self.dtype)
+        pa = PositionArgs.of(self.position.kernel_args())
+        if pa.inv_freq is not None and pa.half_pairing:
+            raise NotImplementedError("this mixer rotates pairs (2i, 2i+1)")
+        ops.qkv_prep(qkv, q, self.q_norm, self.k_norm if n_k else None, pa.inv_freq, cache.k_pages if n_k else None,
+                     cache.v_pages if n_v else None, cache.table, ctx.positions, ctx.row_entry, n_q, n_k, n_v,
+                     s.key_dim, s.value_dim, s.eps, ctx.status)
+        n_splits = self._splits(n, cache)
+        partial = None
+        if n_splits > 1 or ctx.ws.fixed:
+            bound = ops.mapped_attention_partial_floats(min(ctx.ws.max_rows, self.SPLIT_MAX_ROWS), s.n_heads, s.n_maps,
+                                                        s.value_dim, self.MAX_SPLITS)
+            partial = ctx.ws.flat("mattn_partial", ops.mapped_attention_partial_floats(n, s.n_heads, s.n_maps, s.value_dim,
+                                                                                       n_splits), torch.float32, reserve=bound)
+        ops.mapped_attention(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out, s.n_heads,
+                             s.n_maps, s.window, s.keep_first, s.softmax_scale, s.softcap or 0.0, self.lam,
+                             s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits, partial)
+
+    def forward(self, x, ctx, cache):
+        a = ctx.ws.buf("mattn_out", x.shape[0], self.inner_width(), self.dtype)
+        self.core(x, ctx, cache, a)
+        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out", residual=ctx.residual)

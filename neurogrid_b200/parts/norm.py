@@ -47,3 +47,22 @@ class ScalarRMSNorm(RMSNorm):
     def bind(self, t):
         g = t[""].to(device=self.device, dtype=torch.float32).reshape(1)
         self.weight = g.expand(self.spec.size).contiguous()
+
+
+@register("norm", "layernorm")
+class LayerNorm(RMSNorm):
+    """y = (x - mean(x)) * rsqrt(var(x) + eps) * w with the variance as the mean of the squared deviations, a weight
+    and no bias; float32 until the one rounding of y, the residual sum in front as for :class:`RMSNorm`.
+    ``post`` (float32 [H]) is added to the stream after the norm has read it."""
+
+    takes_post = True
+
+    def tensors(self):
+        return {self.spec.tensor: TensorDecl((self.spec.size,), "norm")}
+
+    def bind(self, t):
+        self.weight = t[self.spec.tensor].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def forward(self, h, delta, out, rows=None, post=None):
+        ops.add_layernorm(h, delta, self.weight, out, self.spec.eps, rows, post)
+        return out

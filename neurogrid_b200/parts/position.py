@@ -1,6 +1,8 @@
 """Position encodings, as parameters of the q/k kernel."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionArgs
@@ -20,7 +22,14 @@ class Rope:
         self.spec = spec
         dims = spec.head_dim if spec.rotary_dims is None else spec.rotary_dims
         i = torch.arange(dims // 2, dtype=torch.float64)
-        self.inv_freq = (float(spec.theta) ** (-2.0 * i / max(dims, 1))).to(torch.float32).to(device)
+        f = float(spec.theta) ** (-2.0 * i / max(dims, 1))
+        if spec.freq_scaling is not None:                  # by wavelength: short ones stay, long ones are divided, a blend between
+            factor, low, high, original = (float(v) for v in spec.freq_scaling)
+            wavelength = 2.0 * math.pi / f
+            s = (original / wavelength - low) / (high - low) if high != low else torch.ones_like(f)
+            blend = (1.0 - s) * f / factor + s * f
+            f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blend))
+        self.inv_freq = f.to(torch.float32).to(device)
 
     def kernel_args(self):
         return PositionArgs(self.inv_freq, self.spec.pairing == "half", float(self.spec.scale),

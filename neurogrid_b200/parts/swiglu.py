@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward: down( silu(gate x) * up x )."""
+"""Gated feed-forward: down( act(gate x) * up x ), act = silu (SwiGLU) or the tanh form of gelu."""
 from __future__ import annotations
 
 import torch
@@ -20,29 +20,44 @@ class SwiGLU:
         self.spec, self.dtype, self.device = spec, dtype, device
         self.w_gate_up = self.w_down = None
 
+    def _name(self, role):
+        return self.spec.names[role] + getattr(self.spec, "weight_suffix", ".weight")
+
     def tensors(self):
-        s, n = self.spec, self.spec.names
-        return {f"{n['gate']}.weight": TensorDecl((s.intermediate, s.hidden)),
-                f"{n['up']}.weight": TensorDecl((s.intermediate, s.hidden)),
-                f"{n['down']}.weight": TensorDecl((s.hidden, s.intermediate))}
+        s = self.spec
+        return {self._name("gate"): TensorDecl((s.intermediate, s.hidden)),
+                self._name("up"): TensorDecl((s.intermediate, s.hidden)),
+                self._name("down"): TensorDecl((s.hidden, s.intermediate))}
 
     def bind(self, t):
-        n = self.spec.names
         kw = dict(device=self.device, dtype=self.dtype)
-        self.w_gate_up = torch.cat([t[f"{n['gate']}.weight"].to(**kw), t[f"{n['up']}.weight"].to(**kw)]).contiguous()
-        self.w_down = t[f"{n['down']}.weight"].to(**kw).contiguous()
+        self.w_gate_up = torch.cat([t[self._name("gate")].to(**kw), t[self._name("up")].to(**kw)]).contiguous()
+        self.w_down = t[self._name("down")].to(**kw).contiguous()
 
     def kernels(self):
         return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("elementwise", None)]
 
     def forward(self, x, ctx):
         s = self.spec
-        n = x.shape[0]
-        act = ctx.ws.buf("ffn_act", n, s.intermediate, self.dtype)
-        if ops.gemm_sm100_ok(x, self.w_gate_up):
-            ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the epilogue
-        else:
-            gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
-            ops.linear(x, self.w_gate_up, None, gu)
-            ops.swiglu(gu, act)
+        act = ctx.ws.buf("ffn_act", x.shape[0], s.intermediate, self.dtype)
+        self.gated(x, ctx, act)
         return ops.linear_to_residual(act, self.w_down, None, ctx.ws, "ffn_out", residual=ctx.residual)
+
+    # For a block arrangement that ends mixer and feed-forward with ONE product: the gated activations go into a
+    # block of columns of the caller's buffer, and the caller multiplies by ``out_weight()``.
+    def inner_width(self):
+        return self.spec.intermediate
+
+    def out_weight(self):
+        return self.w_down, None
+
+    def gated(self, x, ctx, act):
+        """act[N, intermediate] (may be a block of columns of a wider buffer) = act(gate x) * (up x)."""
+        s = self.spec
+        activation = getattr(s, "activation", "silu")
+        if ops.gemm_sm100_ok(x, self.w_gate_up):
+            ops.gemm_swiglu_sm100(x, self.w_gate_up, act, activation=activation)    # the gate rides in the epilogue
+        else:
+            gu = ctx.ws.buf("ffn_gate_up", x.shape[0], 2 * s.intermediate, self.dtype)
+            ops.linear(x, self.w_gate_up, None, gu)
+            ops.swiglu(gu, act, activation)

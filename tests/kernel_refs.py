@@ -15,12 +15,12 @@ import torch
 D = torch.float64
 
 
-def embed(table, tokens, out, status, accumulate=False):
+def embed(table, tokens, out, status, accumulate=False, scale=1.0):
     tok = tokens.long()
     bad = (tok < 0) | (tok >= table.shape[0])
     if bad.any():
         status |= 4 if accumulate else 1
-    rows = table[tok.clamp(0, table.shape[0] - 1)].to(torch.float32)
+    rows = (table[tok.clamp(0, table.shape[0] - 1)].to(torch.float32) * torch.tensor(scale, dtype=torch.float32)).to(torch.float32)
     rows[bad] = 0
     out.copy_(out + rows if accumulate else rows)
 
@@ -47,10 +47,103 @@ def residual_add(h, delta):
     h.copy_((h.to(D) + delta.to(D)).to(torch.float32))
 
 
-def swiglu(gate_up, out):
+def swiglu(gate_up, out, activation="silu"):
     I = out.shape[1]
     g, u = gate_up[:, :I].to(D), gate_up[:, I:].to(D)
-    out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+    if activation == "gelu_tanh":
+        a = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    else:
+        a = g / (1 + torch.exp(-g))
+    out.copy_((a * u).to(out.dtype))
+
+
+def add_layernorm(h, delta, weight, out, eps, rows=None, post=None):
+    idx = torch.arange(out.shape[0], device=h.device) if rows is None else rows.long()
+    if delta is not None:
+        if delta.dim() == 3:
+            delta = delta.to(D).sum(0)
+        h[idx] = (h[idx].to(D) + delta[idx].to(D)).to(torch.float32)
+    x = h[idx].to(D)
+    mu = x.mean(-1, keepdim=True)
+    var = ((x - mu) ** 2).mean(-1, keepdim=True)
+    out.copy_(((x - mu) * torch.rsqrt(var + eps) * weight.to(D)).to(out.dtype))
+    if post is not None:
+        h[idx] = (h[idx].to(D) + post.to(D)).to(torch.float32)
+
+
+def qkv_prep(qkv, q_out, q_weight, k_weight, inv_freq, k_pages, v_pages, table, positions, row_entry, n_q, n_k, n_v,
+             dim, vdim, eps, status):
+    n = qkv.shape[0]
+    x = qkv.to(D)
+    q = x[:, : n_q * dim].reshape(n, n_q, dim)
+    k = x[:, n_q * dim:(n_q + n_k) * dim].reshape(n, n_k, dim)
+    v = x[:, (n_q + n_k) * dim:].reshape(n, n_v, vdim)
+
+    def norm(t, w):
+        return t if w is None else t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.to(D)
+
+    def rot(t):
+        if inv_freq is None or inv_freq.numel() == 0:
+            return t
+        r = 2 * inv_freq.numel()
+        ang = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(D)          # float32 angle
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        o = t.clone()
+        a, b = t[..., 0:r:2], t[..., 1:r:2]
+        o[..., 0:r:2], o[..., 1:r:2] = a * c - b * s, b * c + a * s
+        return o
+
+    q, k = rot(norm(q, q_weight)), rot(norm(k, k_weight))
+    valid = row_entry >= 0
+    qo = q.reshape(n, -1).to(q_out.dtype)
+    qo[~valid] = 0
+    q_out.copy_(qo)
+    if n_k or n_v:
+        ps = k_pages.shape[2]
+        for r in range(n):
+            if not bool(valid[r]):
+                continue
+            pos = int(positions[r])
+            page = int(table[int(row_entry[r]), pos // ps])
+            if page < 0 or page >= k_pages.shape[0]:
+                status |= 2
+                continue
+            k_pages[page, :, pos % ps] = k[r].to(k_pages.dtype)
+            v_pages[page, :, pos % ps] = v[r].to(v_pages.dtype)
+
+
+def mapped_attention(q, k_pages, v_pages, table, positions, row_entry, out, n_heads, n_maps, window, keep_first, scale,
+                     softcap, lam, head_norm, post_scale, eps, n_splits=1, partial=None):
+    n = q.shape[0]
+    P, n_k, ps, dim = k_pages.shape
+    n_g, vdim = v_pages.shape[1], v_pages.shape[3]
+    group = n_heads // n_g
+    for r in range(n):
+        e = int(row_entry[r])
+        if e < 0:
+            out[r] = 0
+            continue
+        pos = int(positions[r])
+        lo = max(0, pos - window + 1) if window else 0
+        kp = torch.tensor([j for j in range(pos + 1) if j >= lo or j < keep_first], device=q.device)
+        pages = table[e, kp // ps].long()
+        K = k_pages[pages, :, kp % ps].to(D)             # [keys, n_g * n_maps, dim]
+        Vv = v_pages[pages, :, kp % ps].to(D)            # [keys, n_g, vdim]
+        qr = q[r].to(D).reshape(n_heads, n_maps, dim)
+        o = torch.empty(n_heads, vdim, dtype=D, device=q.device)
+        for h in range(n_heads):
+            g = h // group
+            a = []
+            for m in range(n_maps):
+                s = (K[:, g * n_maps + m] @ qr[h, m]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                a.append(torch.softmax(s, 0) @ Vv[:, g])
+            y = a[0] if n_maps == 1 else a[0] - lam * a[1]
+            if head_norm:
+                y = y * torch.rsqrt((y * y).mean() + eps) * post_scale
+            o[h] = y
+        out[r] = o.reshape(-1).to(out.dtype)
 
 
 def gemm_f32(a, w, bias, out):
@@ -190,7 +283,7 @@ def sample(logits, temperature, top_p, uniform, out, scratch):
 
 
 _NAMES = ["gather_tokens", "embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
-          "attention_generic", "sample"]
+          "attention_generic", "sample", "add_layernorm", "qkv_prep", "mapped_attention"]
 
 
 def install(monkeypatch):
