@@ -1,7 +1,9 @@
 from .lfm2 import ConfigError, Lfm2Config
 from .metanex import MetanexConfig
+from .rofulorn import RofulornConfig
 from .registry import (architecture_name, config_from_dict, load_config, register_architecture,
                        registered_architectures)
-from .specs import (AttentionSpec, InputConvSpec, LatentAttentionSpec, LayerSpec, ModelSpec, MoESpec, NoPositionSpec,
+from .specs import (AttentionSpec, InputConvSpec, LatentAttentionSpec, LayerNormSpec, LayerSpec, MappedAttentionSpec, ModelSpec,
+                    MoESpec, NoPositionSpec,
                     RMSNormSpec, RetentionSpec, RopeSpec, ScalarRMSNormSpec, ScheduleEntry, ShortConvSpec, SwiGLUSpec,
                     TokenSideSpec)

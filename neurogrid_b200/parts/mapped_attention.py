@@ -103,8 +103,10 @@ class MappedAttention:
         longest = cache.table.shape[1] * cache.k_pages.shape[2]
         if s.window:
             longest = min(longest, s.window + s.keep_first)
-        want = -(-2 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))
-        return max(1, min(self.MAX_SPLITS, want, longest // self.SPLIT_MIN_KEYS))
+        most = min(self.MAX_SPLITS, longest // self.SPLIT_MIN_KEYS)
+        if most <= 1:
+            return 1
+        return max(1, min(most, -(-2 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))))
 
     def core(self, x, ctx, cache, out):
         """out[N, n_heads * value_dim] (may be a block of columns of a wider buffer): the heads' outputs."""

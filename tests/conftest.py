@@ -49,3 +49,11 @@ def metanex_dirs(tmp_path_factory):
         out[name + "_calm"] = metanex_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"metanex_{name}c")),
                                                          router_gain=0.05)
     return out
+
+
+@pytest.fixture(scope="session")
+def rofulorn_dirs(tmp_path_factory):
+    """Model folders for the tiny Rofulorn configurations."""
+    import rofulorn_models
+    return {name: rofulorn_models.write_model(cfg, seed, str(tmp_path_factory.mktemp(f"rofulorn_{name}")))
+            for name, (cfg, seed) in rofulorn_models.CONFIGS.items()}

@@ -84,6 +84,27 @@ def softmax_rows(scores, ok):
     return torch.softmax(scores, dim=-1)
 
 
+def attend(q, k, v, mask, scale, softcap=None):
+    """q [T, H, d], k [T, G, d], v [T, G, dv] -> [T, H, dv]: per head softmax(cap(scale q.k)) v over the visible keys,
+    cap(s) = softcap tanh(s / softcap); head h reads key/value head h // (H / G)."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    ok = visible(T, mask)
+    out = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for hd in range(H):
+        g = hd // (H // G)
+        s = (q[:, hd] @ k[:, g].T) * float(scale)
+        if softcap:
+            s = float(softcap) * torch.tanh(s / float(softcap))
+        out[:, hd] = softmax_rows(s, ok) @ v[:, g]
+    return out
+
+
+def combine_maps(a1, a2, lam, diff, eps):
+    """o = a1 - lambda a2, each head's o over its root mean square (eps inside the root), times (1 - diff)."""
+    return over_rms(a1 - lam * a2, eps) * (1.0 - float(diff))
+
+
 def attention_2(h, w, pre, m, positions):
     """Grouped-query attention with a window: q, k rotated; softmax(q.k * scale) v over the window; W_o."""
     T = h.shape[0]
@@ -92,12 +113,7 @@ def attention_2(h, w, pre, m, positions):
     k = (h @ w[pre + "k"].T).view(T, G, d)
     v = (h @ w[pre + "v"].T).view(T, G, dv)
     q, k = rotate(q, positions, m.get("rot")), rotate(k, positions, m.get("rot"))
-    ok = visible(T, m.get("mask"))
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        p = softmax_rows((q[:, hd] @ k[:, g].T) * float(m["scale"]), ok)
-        out[:, hd] = p @ v[:, g]
+    out = attend(q, k, v, m.get("mask"), m["scale"])
     return out.reshape(T, H * dv) @ w[pre + "o"].T, None
 
 
@@ -126,19 +142,8 @@ def diff_attention(h, w, pre, m, positions, eps, kv=None):
     q = over_rms(q, eps) * w[pre + "q.norm"]
     q = rotate(q, positions, m.get("rot")).view(T, H, 2, d)
     k, v = kv if kv is not None else diff_keys_values(h, w, pre, m, positions, eps)
-    ok = visible(T, m.get("mask"))
-    lam = diff_lambda(w, pre, m)
-    cap = m.get("softcap")
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        a = []
-        for mp in range(2):
-            s = (q[:, hd, mp] @ k[:, g, mp].T) * float(m["scale"])
-            if cap:
-                s = float(cap) * torch.tanh(s / float(cap))
-            a.append(softmax_rows(s, ok) @ v[:, g])
-        out[:, hd] = over_rms(a[0] - lam * a[1], eps) * (1.0 - float(m["diff"]))
+    a = [attend(q[:, :, mp], k[:, :, mp], v, m.get("mask"), m["scale"], m.get("softcap")) for mp in range(2)]
+    out = combine_maps(a[0], a[1], diff_lambda(w, pre, m), m["diff"], eps)
     return out.reshape(T, H * dv) @ w[pre + "o"].T + w[pre + "o.b"], (k, v)
 
 
@@ -153,7 +158,7 @@ def forward(cfg, w, tokens, return_stream=False):
     T = tokens.shape[0]
     positions = torch.arange(T)
     eps = float(cfg["norm"]["eps"])
-    x = w["embed"][tokens] * float(cfg["embedding"]["scale"])
+    x = w["embed"][tokens] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     held = {}
     stream = []
     for i, layer in enumerate(cfg["layers"]):
