@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the LFM2-1.2B shape, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex]
+                    [--shape 1.2b|700m|350m] [--prompt-len N] [--workload mixed350m|long700m|metanex|rofulorn]
 
 A "step" is one decode step of the batch.  The default run has the layer sizes of the
 LFM2-1.2B configuration, a batch of 8 and requests that hold 2,048-token prompts and grow
@@ -596,6 +596,63 @@ def metanex_config(width, layers):
             "layers": [dict(pattern[i % 4], mlp=mlp) for i in range(layers)]}
 
 
+def design_arm(arm, cfg, row, args, l2):
+    """One configuration with random weights through the engine's step function: prefill of one 2,048-token prompt
+    in one step, then decode at batch 8 and 1 after 2,048 tokens; fills ``row`` under the arm's name and returns
+    the engine.  CUDA events; the L2 is flushed between timed steps."""
+    import torch
+    from neurogrid_b200 import Engine
+    from neurogrid_b200.engine import StepEntry
+    eng = Engine(config=cfg, random_weights=0, dtype="bf16", max_seq_len=8192, max_requests=8,
+                 max_tokens_per_step=2048, num_pages=8 * 4096 // 16)
+    r = eng.runner
+    V = eng.model.spec.vocab_size
+    g = torch.Generator().manual_seed(1)
+    toks = lambda n: torch.randint(0, V, (n,), generator=g).tolist()
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            flush_l2(l2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return median(ts)
+
+    # prefill: one request's 2,048-token prompt in one step (the third meeting of the shape replays its graph)
+    n_pre = [0]
+
+    def prefill():
+        rid = ("p", n_pre[0])
+        n_pre[0] += 1
+        r.step([StepEntry(rid, toks(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+        r.finish(rid)
+
+    for _ in range(3):
+        prefill()
+    torch.cuda.synchronize()
+    ms = timed(prefill, 5)
+    row[arm + "_prefill_ms"] = round(ms, 3)
+    row[arm + "_prefill_tok_s"] = round(PREFILL_TOKENS / ms * 1e3)
+    # decode: 8 requests (and 1) that hold 2,048 tokens each, one token a step
+    for i in range(8):
+        r.step([StepEntry(("d", i), toks(PREFILL_TOKENS), [])])
+    for batch in (8, 1):
+        step = lambda: r.step([StepEntry(("d", i), toks(1), [0]) for i in range(batch)])
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        ms = timed(step, 24)
+        row[f"{arm}_decode{batch}_ms"] = round(ms, 4)
+        row[f"{arm}_decode{batch}_tok_s"] = round(batch / ms * 1e3)
+    r.check_status()
+    row[arm + "_weights_gb"] = round(eng.model.weight_bytes() / 1e9, 3)
+    return eng
+
+
 def run_metanex(args):
     """Prefill and decode throughput of the Metanex design at layer sizes of a real model, beside LFM2 (the closest
     existing model: a hybrid of state layers and attention layers) at equal width and depth, and the design's own
@@ -615,56 +672,10 @@ def run_metanex(args):
         arms = {"metanex": metanex_config(width, layers), "lfm2": lfm2}
         row = {"width": width, "layers": layers}
         for arm, cfg in arms.items():
-            eng = Engine(config=cfg, random_weights=0, dtype="bf16", max_seq_len=8192, max_requests=8,
-                         max_tokens_per_step=2048, num_pages=8 * 4096 // 16)
-            r = eng.runner
-            V = eng.model.spec.vocab_size
-            g = torch.Generator().manual_seed(1)
-            toks = lambda n: torch.randint(0, V, (n,), generator=g).tolist()
-
-            def timed(fn, reps):
-                ts = []
-                for _ in range(reps):
-                    flush_l2(l2)
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    fn()
-                    b.record()
-                    torch.cuda.synchronize()
-                    ts.append(a.elapsed_time(b))
-                return median(ts)
-
-            # prefill: one request's 2,048-token prompt in one step (the third meeting of the shape replays its graph)
-            n_pre = [0]
-
-            def prefill():
-                rid = ("p", n_pre[0])
-                n_pre[0] += 1
-                r.step([StepEntry(rid, toks(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
-                r.finish(rid)
-
-            for _ in range(3):
-                prefill()
-            torch.cuda.synchronize()
-            ms = timed(prefill, 5)
-            row[arm + "_prefill_ms"] = round(ms, 3)
-            row[arm + "_prefill_tok_s"] = round(PREFILL_TOKENS / ms * 1e3)
-            # decode: 8 requests (and 1) that hold 2,048 tokens each, one token a step
-            for i in range(8):
-                r.step([StepEntry(("d", i), toks(PREFILL_TOKENS), [])])
-            for batch in (8, 1):
-                step = lambda: r.step([StepEntry(("d", i), toks(1), [0]) for i in range(batch)])
-                for _ in range(max(3, args.warmup)):
-                    step()
-                torch.cuda.synchronize()
-                ms = timed(step, 24)
-                row[f"{arm}_decode{batch}_ms"] = round(ms, 4)
-                row[f"{arm}_decode{batch}_tok_s"] = round(batch / ms * 1e3)
-            r.check_status()
-            row[arm + "_weights_gb"] = round(eng.model.weight_bytes() / 1e9, 3)
+            eng = design_arm(arm, cfg, row, args, l2)
             if arm == "metanex" and not args.no_kernels:
                 row["kernels"] = metanex_kernel_times(eng, l2, pk)
-            del eng, r
+            del eng
             torch.cuda.empty_cache()
         results.append(row)
     time.sleep(0.06)
@@ -783,6 +794,154 @@ def metanex_kernel_times(eng, l2, pk):
 
 
 
+# ---------------------------------------------------------------------------------------------- --workload rofulorn
+def rofulorn_config(width, layers, ff):
+    """A Rofulorn configuration with layers of a real model's sizes: plain windowed attention layers (heads of 64,
+    four query heads to a key/value head) alternate with two-map attention layers (half as many heads, values of
+    128), every fourth layer reading the keys and values of the two-map layer two before it; windows of 1,024
+    tokens, four kept first tokens; a gated feed-forward as wide as LFM2's at the same width."""
+    heads = width // 64
+    a2 = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 64, "scale": 0.125,
+                                           "mask": {"size": 1024}, "rot": {"dims": 32, "base": 1000000.0}}}
+    diff = {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": 64, "vdim": 128, "scale": 0.125, "softcap": 30.0,
+            "diff": 0.5, "mask": {"size": 1024, "keep_first": 4},
+            "rot": {"dims": 32, "base": 20000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            layer = dict(a2)
+        else:
+            layer = {"type": "attention", "mixer": dict(diff, **({"kv_from": i - 2} if i % 4 == 3 else {}))}
+        out.append(dict(layer, mlp={"kind": "dense", "ff": ff}))
+    return {"architecture": "Rofulorn", "vocab": 65536, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
+            "layers": out}
+
+
+def run_rofulorn(args):
+    """Prefill and decode throughput of the Rofulorn design at layer sizes of a real model, beside LFM2 (the closest
+    existing model: grouped-query attention layers with a gated feed-forward) at equal width, depth and feed-forward
+    width, and the design's attention kernels alone beside LFM2's.  One JSON line.  Random weights, synthetic token
+    ids; CUDA events; the L2 is flushed between timed steps."""
+    import torch
+    pk = peaks()
+    l2 = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda:0")
+    clocks = ClockSampler(0)
+    clocks.start()
+    results = []
+    for width, layers in ((1024, 16), (2048, 16)):
+        lfm2 = dict(LFM2_1_2B)
+        lfm2.update(SHAPES["350m" if width == 1024 else "1.2b"])
+        row = {"width": width, "layers": layers}
+        for arm, cfg in {"rofulorn": rofulorn_config(width, layers, ffn_width(lfm2)), "lfm2": lfm2}.items():
+            eng = design_arm(arm, cfg, row, args, l2)
+            if not args.no_kernels:
+                row[arm + "_kernels"] = attention_kernel_times(eng, l2, pk)
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    time.sleep(0.06)
+    clocks.stop()
+    print(json.dumps({"workload": "rofulorn", "what": "Rofulorn beside LFM2 at equal width, depth and feed-forward width: "
+                      "prefill of 2,048 tokens, decode at batch 8 and 1 after 2,048 tokens; attention kernels alone",
+                      "results": results, "dtype": "bf16", "data": "synthetic token ids, random-init weights", "peaks": pk,
+                      "clocks": clocks.summary(), "impl": "ours"}))
+
+
+def attention_kernel_times(eng, l2, pk):
+    """Every attention layer kind of the model alone, through the mixer's own launch plan: the q/k preparation with
+    the page write, and the attention core, for a 2,048-token portion and for 8 single tokens after 2,048 (CUDA
+    events around the launches, L2 flushed before, median of 7): microseconds, the multiply-adds of the two products
+    as TFLOP/s with the fraction of the measured tensor peak, and the bytes a decode step must read with the fraction
+    of the measured copy bandwidth."""
+    import torch
+    from neurogrid_b200.csrc import ops
+    from neurogrid_b200.parts import PagedView, StepContext
+    from neurogrid_b200.parts.base import Workspace
+    model, dev = eng.model, eng.device
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, generator=g, device=dev).to(torch.bfloat16)
+
+    def timed(fn):
+        ts = []
+        for _ in range(9):
+            flush_l2(l2)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return median(ts[2:])
+
+    out = {"unit": "us"}
+    seen = set()
+    for blk in model.blocks:
+        mixer = blk.mixer
+        kind = type(mixer).__name__
+        s = mixer.spec
+        if kind not in ("MappedAttention", "Attention") or not mixer.owns_cache:
+            continue
+        maps = getattr(s, "n_maps", 1)
+        d = getattr(s, "key_dim", None) or s.head_dim
+        dv = getattr(s, "value_dim", None) or s.head_dim
+        tag = f"{kind}_{maps}map_{s.n_heads}x{d}"
+        if tag in seen:
+            continue
+        seen.add(tag)
+        need = mixer.cache_need()
+        ps, n_pages = 16, 8 * 4096 // 16
+        vh, vd = need.value_shape()
+        kp, vp = rnd(n_pages, need.n_kv_heads, ps, need.head_dim), rnd(n_pages, vh, ps, vd)
+        for rows, entries in ((PREFILL_TOKENS, 1), (8, 8)):
+            q_len = rows // entries
+            before = 0 if entries == 1 else 2048
+            table = torch.arange(entries * 256, dtype=torch.int32, device=dev).view(entries, 256)
+            ctx = StepContext(n_rows=rows, n_entries=entries, max_q=q_len, tokens=i32([0] * rows),
+                              positions=i32([before + t for e in range(entries) for t in range(q_len)]),
+                              row_entry=i32([e for e in range(entries) for _ in range(q_len)]),
+                              cu_q=i32([q_len * e for e in range(entries + 1)]), ctx_before=i32([before] * entries),
+                              slots=i32(list(range(entries))), status=torch.zeros(1, dtype=torch.int32, device=dev),
+                              ws=Workspace(4096, dev), dtype=torch.bfloat16, q_lens=[q_len] * entries,
+                              ctx_lens=[before] * entries, slot_ids=list(range(entries)))
+            view = PagedView(kp, vp, table)
+            o = torch.empty(rows, s.n_heads * dv, dtype=torch.bfloat16, device=dev)
+            if kind == "MappedAttention":
+                qkv = rnd(rows, mixer.w_qkv.shape[0])
+                qb = torch.empty(rows, s.n_heads * maps * d, dtype=torch.bfloat16, device=dev)
+                pa = mixer.position.kernel_args()
+                prep = lambda: ops.qkv_prep(qkv, qb, mixer.q_norm, mixer.k_norm, pa.inv_freq, kp, vp, table, ctx.positions,
+                                            ctx.row_entry, s.n_heads * maps, need.n_kv_heads, vh, d, dv, s.eps, ctx.status)
+                core = lambda: mixer.attend(qb, view, ctx, o)
+            else:
+                qkv = rnd(rows, mixer.w_qkv.shape[0])
+                qb = torch.empty(rows, s.n_heads * d, dtype=torch.bfloat16, device=dev)
+                pa = mixer.position.kernel_args()
+                prep = lambda: ops.rope_cache(qkv, qb, mixer.q_norm, mixer.k_norm, pa.inv_freq, pa.half_pairing, pa.pos_scale, kp,
+                                              vp, table, ctx.positions, ctx.row_entry, s.n_heads, s.n_kv_heads, d, s.qk_norm_eps,
+                                              ctx.status)
+                core = lambda: mixer.attend(qb, view, ctx, o)
+            prep()
+            core()
+            torch.cuda.synchronize()
+            name = ("prefill2048_" if entries == 1 else "decode8_") + tag
+            window = getattr(s, "window", None)
+            if entries == 1:
+                pairs = sum(min(t + 1, window) if window else t + 1 for t in range(rows))
+            else:
+                pairs = rows * (min(before + 1, window) if window else before + 1)
+            flops = 2 * pairs * s.n_heads * (maps * d + maps * dv)
+            keys = min(before + q_len, window) if window else before + q_len
+            kv_bytes = entries * keys * need.elements_per_token() * 2
+            us_p, us_c = timed(prep), timed(core)
+            out[name] = {"prep_us": round(us_p, 2), "core_us": round(us_c, 2), "core_flops": int(flops),
+                         "core_tflops": round(flops / (us_c * 1e-6) / 1e12, 2),
+                         "core_of_tensor_peak": round(flops / (us_c * 1e-6) / 1e12 / pk["bf16_tflops"], 4),
+                         "kv_bytes": int(kv_bytes),
+                         "core_of_copy_bandwidth": round(kv_bytes / (us_c * 1e-6) / (pk["hbm_gbs"] * 1e9), 4)}
+    return out
+
+
 def run_reference(args):
     """The reference's own library through its stock entry points; same metric, same line."""
     shape_name = SHAPE_NAMES[args.shape]
@@ -845,9 +1004,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="tokens each request holds before decoding (default 2,048; the context is twice this)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex"],
-                    help="run another workload of the benchmark set through Engine.generate instead; metanex: the "
-                         "Metanex design beside LFM2 at equal width and depth, prefill and decode, and its kernels alone")
+    ap.add_argument("--workload", default="", choices=["", "mixed350m", "long700m", "metanex", "rofulorn"],
+                    help="run another workload of the benchmark set through Engine.generate instead; metanex / rofulorn: "
+                         "that design beside LFM2 at equal width and depth, prefill and decode, and its kernels alone")
     ap.add_argument("--repeat", type=int, default=2, help="--workload: runs (the first also warms up and captures graphs)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel timings")
     ap.add_argument("--profile-only", action="store_true",
@@ -864,6 +1023,9 @@ def main():
         args.warmup = 3
     if args.workload == "metanex":
         run_metanex(args)
+        return 0
+    if args.workload == "rofulorn":
+        run_rofulorn(args)
         return 0
     if args.workload:
         run_workload(args)

@@ -36,7 +36,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "gemm_sm100": (),
     "attention_sm100": (),
     "input_conv": (), "retention": (), "latent": (), "latent_mma": (), "moe": (), "token_side": (),
-    "mapped_attention": (),
+    "mapped_attention": (), "mapped_attention_mma": (),
 }
 
 _lock = threading.RLock()
@@ -180,4 +180,5 @@ def build_all(extra: Sequence[Tuple[str, Mapping[str, object]]] = (), *, verbose
 
 # sources that only exist as ``-D`` specialisations (never built bare)
 SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",), "shortconv": ("NG_CONV_L",),
-                                         "rope_cache": ("NG_ROPE_PAIRS",), "latent_mma": ("NG_LAT_RANK",)}
+                                         "rope_cache": ("NG_ROPE_PAIRS",), "latent_mma": ("NG_LAT_RANK",),
+                                         "mapped_attention_mma": ("NG_MA_D", "NG_MA_DV")}

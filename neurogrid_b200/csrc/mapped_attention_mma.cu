@@ -1,0 +1,306 @@
+// The attention of mapped_attention.cu for long bfloat16 steps, on the tensor cores (mma.sync m16n8k16).
+//
+// Same mathematics: float32 scores, float32 online softmax, float32 weights.  The products run on the tensor cores
+// without giving that up: q and k are bfloat16 as the cache holds them, so q.k is a float32 sum of exact products;
+// a float32 weight p enters the weighted sum as three bfloat16 terms hi + mid + lo (what is left is below 2^-24 p),
+// each term's products with the bfloat16 values exact in the float32 accumulators.
+//
+// A block takes consecutive rows of one entry and one query head: 64 rows (one map) or 32 rows (two maps; a warp
+// per map and 16 rows, the maps combined in the epilogue), and walks the keys the block's rows can see, kept first
+// tokens then the window, in tiles of 64: keys (of each map) and values are staged once in shared memory for the four
+// warps (16-byte copies, page by page through the block table), S = Q K^T in registers, mask and cap per element,
+// P V with P straight from the accumulators' layout, values through ldmatrix.trans.  Specialised on the key and
+// value sizes (-DNG_MA_D, -DNG_MA_DV: multiples of 16, up to 128).
+#include "ng_common.cuh"
+
+#if !defined(NG_MA_D) || !defined(NG_MA_DV)
+#error "compile with -DNG_MA_D=<key size> -DNG_MA_DV=<value size>"
+#endif
+static_assert(NG_MA_D % 16 == 0 && NG_MA_D >= 16 && NG_MA_D <= 128, "key size: a multiple of 16 up to 128");
+static_assert(NG_MA_DV % 16 == 0 && NG_MA_DV >= 16 && NG_MA_DV <= 128, "value size: a multiple of 16 up to 128");
+
+typedef __nv_bfloat16 bf16;
+constexpr int D = NG_MA_D, DV = NG_MA_DV;
+constexpr int KT = 64, WARPS = 4, THREADS = 128;
+constexpr int QP = D + 8, KP = D + 8, VP = DV + 8;      // row pitches in elements: 16 bytes of padding against bank conflicts
+
+struct MmaParams {
+    const bf16* q; const bf16* k_pages; const bf16* v_pages; const int* table; int table_stride;
+    const int* cu_q; const int* ctx_before; bf16* out; int out_ld;
+    int nH, nG, page_size, num_pages, window, keep_first;
+    float scale, softcap, lambda, post_scale, eps; int head_norm;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float x, float y) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// p = hi + mid + lo in bfloat16 terms, two weights at a time
+__device__ __forceinline__ void split3(float x, float y, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+    const float xh = __bfloat162float(__float2bfloat16_rn(x)), yh = __bfloat162float(__float2bfloat16_rn(y));
+    const float xr = x - xh, yr = y - yh;
+    const float xm = __bfloat162float(__float2bfloat16_rn(xr)), ym = __bfloat162float(__float2bfloat16_rn(yr));
+    hi = pack2(xh, yh);
+    mid = pack2(xm, ym);
+    lo = pack2(xr - xm, yr - ym);
+}
+
+template <int M>
+__global__ void __launch_bounds__(THREADS)
+mapped_attention_mma_kernel(const MmaParams p) {
+    constexpr int ROWS = (WARPS / M) * 16;               // rows of a block
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                        // [M][ROWS][QP]
+    bf16* Ks = Qs + M * ROWS * QP;                                       // [M][KT][KP]
+    bf16* Vs = Ks + M * KT * KP;                                         // [KT][VP]
+    float* Os = reinterpret_cast<float*>(Ks);                            // epilogue: [M][ROWS][DV], over the tiles
+    __shared__ int kpos_s[KT];
+    __shared__ long long koff_s[KT];                                     // element offset of the key's page slot, -1: none
+    ng_pdl_trigger();
+    const int entry = blockIdx.y, head = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q0 = p.cu_q[entry], q_len = p.cu_q[entry + 1] - q0;
+    const int r0 = blockIdx.x * ROWS;                    // first row of the block within the entry
+    ng_pdl_wait();
+    if (r0 >= q_len) return;
+    const int before = p.ctx_before[entry];
+    const int n_rows = min(ROWS, q_len - r0);
+    const int g = head / (p.nH / p.nG);
+    const int map = M == 2 ? (warp & 1) : 0;
+    const int wt = M == 2 ? (warp >> 1) : warp;          // the warp's tile of 16 rows
+    const bf16* qg = ng_after_wait(p.q);
+    // ---- Q: rows r0.., both maps, into shared memory (rows beyond the entry: zeros)
+    for (int i = tid; i < M * ROWS * (D / 8); i += THREADS) {
+        const int ch = i % (D / 8), row = (i / (D / 8)) % ROWS, m = i / ((D / 8) * ROWS);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_rows)
+            v = *reinterpret_cast<const uint4*>(qg + ((size_t)(q0 + r0 + row) * p.nH + head) * M * D + (size_t)m * D + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + ((size_t)m * ROWS + row) * QP + ch * 8) = v;
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldsm_x4(qf[ks], Qs + ((size_t)map * ROWS + wt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + ks * 16 + (lane >> 4) * 8);
+    // ---- the keys the block's rows see: kept first tokens [0, n_sink), then [lo, last position]
+    const int pos_first = before + r0, pos_last = before + r0 + n_rows - 1;
+    const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int n_sink = min(p.keep_first, lo);
+    const int n_keys = n_sink + (pos_last - lo + 1);
+    const int gq = lane >> 2, tq = lane & 3;
+    const int row_a = wt * 16 + gq, row_b = row_a + 8;   // this thread's two rows within the block
+    const int pos_a = pos_first + row_a, pos_b = pos_first + row_b;
+    const int w_first = pos_first + wt * 16, w_last = min(pos_last, w_first + 15);   // the warp's positions
+    const bool warp_live = wt * 16 < n_rows;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const int* trow = p.table + (size_t)entry * p.table_stride;
+
+    for (int t0 = 0; t0 < n_keys; t0 += KT) {
+        __syncthreads();                                 // the tile before is done with
+        if (tid < KT) {
+            const int t = t0 + tid;
+            int kpos = -1;
+            long long off = -1;
+            if (t < n_keys) {
+                kpos = t < n_sink ? t : lo + (t - n_sink);
+                const int page = trow[kpos / p.page_size];
+                if (page >= 0 && page < p.num_pages) off = (long long)page * p.page_size + (kpos % p.page_size);
+                else kpos = -1;
+            }
+            kpos_s[tid] = kpos;
+            koff_s[tid] = off;
+        }
+        __syncthreads();
+        for (int i = tid; i < M * KT * (D / 8); i += THREADS) {
+            const int ch = i % (D / 8), key = (i / (D / 8)) % KT, m = i / ((D / 8) * KT);
+            const long long off = koff_s[key];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (off >= 0) {
+                const long long page = off / p.page_size, slot = off % p.page_size;
+                v = *reinterpret_cast<const uint4*>(p.k_pages + (((size_t)page * p.nG * M + (size_t)g * M + m) * p.page_size + slot) * D + ch * 8);
+            }
+            *reinterpret_cast<uint4*>(Ks + ((size_t)m * KT + key) * KP + ch * 8) = v;
+        }
+        for (int i = tid; i < KT * (DV / 8); i += THREADS) {
+            const int ch = i % (DV / 8), key = i / (DV / 8);
+            const long long off = koff_s[key];
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (off >= 0) {
+                const long long page = off / p.page_size, slot = off % p.page_size;
+                v = *reinterpret_cast<const uint4*>(p.v_pages + (((size_t)page * p.nG + g) * p.page_size + slot) * DV + ch * 8);
+            }
+            *reinterpret_cast<uint4*>(Vs + (size_t)key * VP + ch * 8) = v;
+        }
+        __syncthreads();
+        // does any row of the warp see any key of the tile?  (positions ascend within both parts of the list)
+        bool any = warp_live;
+        if (any) {
+            const int t_last = min(n_keys, t0 + KT) - 1;
+            const int k_first = t0 < n_sink ? t0 : lo + (t0 - n_sink);
+            const int k_last = t_last < n_sink ? t_last : lo + (t_last - n_sink);
+            const bool sink_part = t0 < n_sink;
+            const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;     // lowest window key of the warp's rows
+            any = k_first <= w_last && (sink_part || k_last >= w_lo || k_first < p.keep_first);
+        }
+        if (!any) continue;
+        // ---- S = Q K^T
+        float s[KT / 8][4];
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        const bf16* kt = Ks + (size_t)map * KT * KP;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+            for (int jp = 0; jp < KT / 16; ++jp) {
+                uint32_t b[4];
+                ldsm_x4(b, kt + ((size_t)jp * 16 + (lane & 7) + (lane >> 4) * 8) * KP + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[2 * jp], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * jp + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // ---- scale, cap, mask; online softmax in float32
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kpos = kpos_s[j * 8 + 2 * tq + (e & 1)];
+                const int pos = (e < 2) ? pos_a : pos_b;
+                const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
+                const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
+                float v = s[j][e] * p.scale;
+                if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+                v = vis ? v : -INFINITY;
+                s[j][e] = v;
+                if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ca = m_a == -INFINITY ? 0.f : expf(m_a - mn_a), cb = m_b == -INFINITY ? 0.f : expf(m_b - mn_b);
+        const float ua = mn_a == -INFINITY ? 0.f : mn_a, ub = mn_b == -INFINITY ? 0.f : mn_b;
+        m_a = mn_a; m_b = mn_b;
+        l_a *= ca; l_b *= cb;
+#pragma unroll
+        for (int j = 0; j < DV / 8; ++j) { o[j][0] *= ca; o[j][1] *= ca; o[j][2] *= cb; o[j][3] *= cb; }
+#pragma unroll
+        for (int j = 0; j < KT / 8; ++j) {
+            s[j][0] = expf(s[j][0] - ua); s[j][1] = expf(s[j][1] - ua);        // exp(-inf) = 0 for what the mask hides
+            s[j][2] = expf(s[j][2] - ub); s[j][3] = expf(s[j][3] - ub);
+            l_a += s[j][0] + s[j][1];
+            l_b += s[j][2] + s[j][3];
+        }
+        // ---- O += P V, P as three bfloat16 terms
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t ah[4], am[4], al[4];
+            split3(s[2 * kk][0], s[2 * kk][1], ah[0], am[0], al[0]);
+            split3(s[2 * kk][2], s[2 * kk][3], ah[1], am[1], al[1]);
+            split3(s[2 * kk + 1][0], s[2 * kk + 1][1], ah[2], am[2], al[2]);
+            split3(s[2 * kk + 1][2], s[2 * kk + 1][3], ah[3], am[3], al[3]);
+#pragma unroll
+            for (int np = 0; np < DV / 16; ++np) {
+                uint32_t b[4];
+                ldsm_x4_t(b, Vs + ((size_t)kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + np * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * np], al, b[0], b[1]);
+                mma_bf16(o[2 * np + 1], al, b[2], b[3]);
+                mma_bf16(o[2 * np], am, b[0], b[1]);
+                mma_bf16(o[2 * np + 1], am, b[2], b[3]);
+                mma_bf16(o[2 * np], ah, b[0], b[1]);
+                mma_bf16(o[2 * np + 1], ah, b[2], b[3]);
+            }
+        }
+    }
+    // ---- epilogue: each map's a = O / l into shared memory, then the maps combined row by row
+    __syncthreads();                                     // every warp has left the tiles
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float ia = l_a > 0.f ? 1.f / l_a : 0.f, ib = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+    for (int j = 0; j < DV / 8; ++j) {
+        float* oa = Os + ((size_t)map * ROWS + row_a) * DV + j * 8 + 2 * tq;
+        float* ob = Os + ((size_t)map * ROWS + row_b) * DV + j * 8 + 2 * tq;
+        oa[0] = o[j][0] * ia; oa[1] = o[j][1] * ia;
+        ob[0] = o[j][2] * ib; ob[1] = o[j][3] * ib;
+    }
+    __syncthreads();
+    for (int row = warp; row < n_rows; row += WARPS) {
+        float v[DV / 32 + 1];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < DV / 32 + 1; ++u) {
+            const int c = lane + 32 * u;
+            v[u] = 0.f;
+            if (c < DV) {
+                v[u] = Os[(size_t)row * DV + c];
+                if (M == 2) v[u] -= p.lambda * Os[((size_t)ROWS + row) * DV + c];
+                ss += v[u] * v[u];
+            }
+        }
+        float r = 1.f;
+        if (p.head_norm) r = rsqrtf(ng_warp_sum(ss) / (float)DV + p.eps) * p.post_scale;
+        bf16* dst = p.out + (size_t)(q0 + r0 + row) * p.out_ld + (size_t)head * DV;
+#pragma unroll
+        for (int u = 0; u < DV / 32 + 1; ++u) {
+            const int c = lane + 32 * u;
+            if (c < DV) dst[c] = __float2bfloat16_rn(v[u] * r);
+        }
+    }
+}
+
+template <int M>
+static int mma_launch(const MmaParams& p, int n_entries, int max_q, cudaStream_t stream) {
+    constexpr int ROWS = (WARPS / M) * 16;
+    const size_t tiles = ((size_t)M * ROWS * QP + (size_t)M * KT * KP + (size_t)KT * VP) * sizeof(bf16);
+    const size_t epi = (size_t)M * ROWS * QP * sizeof(bf16) + (size_t)M * ROWS * DV * sizeof(float);
+    const size_t smem = tiles > epi ? tiles : epi;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(mapped_attention_mma_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        attr = true;
+    }
+    dim3 grid((max_q + ROWS - 1) / ROWS, n_entries, p.nH);
+    if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
+    NG_LAUNCH((mapped_attention_mma_kernel<M>), grid, THREADS, smem, stream, p);
+    return ng_launch_status();
+}
+
+// q [N, nH * n_maps * D] bfloat16; keys [P, nG * n_maps, page, D]; values [P, nG, page, DV]; out rows out_ld apart.
+// Rows are named by cu_q (first row of each entry) and ctx_before (tokens of the request before the step).
+NG_EXPORT int ng_mapped_attention_mma(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                      int table_stride, const int* cu_q, const int* ctx_before, void* out, int out_ld,
+                                      int n_entries, int max_q, int nH, int nG, int n_maps, int d, int dv, int page_size,
+                                      int num_pages, int window, int keep_first, float scale, float softcap, float lambda,
+                                      float post_scale, float eps, int head_norm, cudaStream_t stream) {
+    if (n_entries <= 0 || max_q <= 0) return NG_OK;
+    if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || page_size <= 0 || n_maps < 1 || n_maps > 2 || out_ld < nH * dv ||
+        window < 0 || keep_first < 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        return NG_BAD_SIZE;
+    MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, (bf16*)out,
+                out_ld, nH, nG, page_size, num_pages, window, keep_first, scale, softcap, lambda, post_scale, eps, head_norm};
+    return n_maps == 2 ? mma_launch<2>(p, n_entries, max_q, stream) : mma_launch<1>(p, n_entries, max_q, stream);
+}

@@ -451,6 +451,38 @@ def mapped_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
              _act_flag(q, "q"), _stream()), "mapped_attention")
 
 
+MAPPED_BACKEND = os.environ.get("NEUROGRID_B200_MAPPED", "mma")     # "mma": tensor-core kernel for long bfloat16 steps; "ffma"
+
+
+def mapped_attention_mma_takes(dim: int, vdim: int, dtype) -> bool:
+    """Whether the tensor-core kernel takes these sizes (bfloat16; key and value sizes multiples of 16 up to 128)."""
+    return MAPPED_BACKEND == "mma" and dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 \
+        and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                         cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
+                         n_heads: int, n_maps: int, window: Optional[int], keep_first: int, scale: float, softcap: float,
+                         lam: float, head_norm: bool, post_scale: float, eps: float) -> None:
+    """``mapped_attention`` for long bfloat16 steps on the tensor cores: scores are float32 sums of exact bfloat16
+    products, the float32 softmax weights enter the weighted sum as three bfloat16 terms each.  Rows are named by
+    ``cu_q`` [R+1] and ``ctx_before`` [R]; ``max_q`` bounds the longest entry."""
+    n = q.shape[0]
+    num_pages, n_k, page_size, dim = k_pages.shape
+    n_g, vdim = v_pages.shape[1], v_pages.shape[3]
+    if n_k != n_g * n_maps or q.shape != (n, n_heads * n_maps * dim) or out.shape != (n, n_heads * vdim) \
+            or q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or v_pages.dtype != torch.bfloat16 \
+            or out.dtype != torch.bfloat16 or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+        raise KernelError("mapped_attention_mma: shapes or dtypes do not fit")
+    _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
+    f = _fn("mapped_attention_mma", "ng_mapped_attention_mma", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 12
+            + [_c_float] * 5 + [_c_int, _c_void_p], {"NG_MA_D": dim, "NG_MA_DV": vdim})
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
+             out.data_ptr(), _column_block(out, "attention out"), n_entries, max_q, n_heads, n_g, n_maps, dim, vdim,
+             page_size, num_pages, int(window or 0), int(keep_first), float(scale), float(softcap or 0.0), float(lam),
+             float(post_scale), float(eps), int(bool(head_norm)), _stream()), "mapped_attention_mma")
+
+
 # ----------------------------------------------------------------------------- input convolution
 def input_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
                ctx_before: torch.Tensor, slots: torch.Tensor, n_entries: int, max_q: int) -> None:

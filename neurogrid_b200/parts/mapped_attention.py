@@ -22,7 +22,9 @@ class MappedAttention:
     softmax weights, their sums with the values, norms, angles and lambda are float32 in both compute dtypes.
 
     ``owns_cache`` False builds a layer that reads another layer's keys and values: it has no k/v tensors.
-    Steps of few rows cut every row's keys into runs (a block each) so that the GPU is filled.
+    Steps of few rows (and the float32 path) run a kernel with a block per row and head and cut every row's keys
+    into runs so that the GPU is filled; longer bfloat16 steps run the tensor-core kernel (the float32 weights as
+    three bfloat16 terms) when the head sizes are multiples of 16 up to 128.
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
@@ -82,7 +84,11 @@ class MappedAttention:
                          keep_first=s.cache_keep_first if s.cache_window else 0)
 
     def kernels(self):
-        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("mapped_attention", None)]
+        s = self.spec
+        jobs = [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("mapped_attention", None)]
+        if ops.mapped_attention_mma_takes(s.key_dim, s.value_dim, self.dtype):
+            jobs.append(("mapped_attention_mma", {"NG_MA_D": s.key_dim, "NG_MA_DV": s.value_dim}))
+        return jobs
 
     def scratch_bytes_per_row(self):
         s = self.spec
@@ -130,6 +136,17 @@ class MappedAttention:
         ops.qkv_prep(qkv, q, self.q_norm, self.k_norm if n_k else None, pa.inv_freq, cache.k_pages if n_k else None,
                      cache.v_pages if n_v else None, cache.table, ctx.positions, ctx.row_entry, n_q, n_k, n_v,
                      s.key_dim, s.value_dim, s.eps, ctx.status)
+        self.attend(q, cache, ctx, out)
+
+    def attend(self, q, cache, ctx, out):
+        """The attention core over the pages: q [N, n_heads * n_maps * key_dim] as the preparation left it."""
+        s = self.spec
+        n = q.shape[0]
+        if n > self.SPLIT_MAX_ROWS and ops.mapped_attention_mma_takes(s.key_dim, s.value_dim, self.dtype):
+            ops.mapped_attention_mma(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                                     ctx.n_entries, ctx.max_q, s.n_heads, s.n_maps, s.window, s.keep_first,
+                                     s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps)
+            return
         n_splits = self._splits(n, cache)
         partial = None
         if n_splits > 1 or ctx.ws.fixed:

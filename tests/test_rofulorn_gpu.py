@@ -120,7 +120,7 @@ def _pages(n_tokens, ps, n_k, dim, n_v, vdim, dtype, seed=0, shuffle=True):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("dim,vdim,rot_dims", [(16, 24, 8), (10, 5, 4), (64, 64, 64), (48, 96, 0), (130, 40, 32)])
+@pytest.mark.parametrize("dim,vdim,rot_dims", [(16, 24, 8), (10, 5, 4), (64, 64, 64), (40, 72, 0), (130, 40, 32)])
 def test_norm_rotation_and_page_write(dtype, dim, vdim, rot_dims):
     n_q, n_k, n_v, T, ps = 6, 4, 2, 37, 8
     qkv = _x((T, (n_q + n_k) * dim + n_v * vdim), dtype, scale=2.0)
@@ -159,7 +159,7 @@ def _attention_case(dtype, T, H, G, M, dim, vdim, window, keep, softcap, ps, tar
     return r(q), r(k), r(v)
 
 
-def _run_core(dtype, q, k, v, window, keep, softcap, ps, scale, lam, norm, cuts, splits_from=None):
+def _run_core(dtype, q, k, v, window, keep, softcap, ps, scale, lam, norm, cuts, splits_from=None, mma=False):
     T, H, M, dim = q.shape
     G, vdim = v.shape[1], v.shape[2]
     o = ops()
@@ -173,8 +173,12 @@ def _run_core(dtype, q, k, v, window, keep, softcap, ps, scale, lam, norm, cuts,
         n_splits = splits_from(n) if splits_from else 1
         partial = torch.empty(max(1, o.mapped_attention_partial_floats(n, H, M, vdim, n_splits)), device=DEV) if n_splits > 1 else None
         out = torch.full((n, H * vdim + 16), 9.0, dtype=dtype, device=DEV)
-        o.mapped_attention(qo, kp, vp, table, ctx.positions, ctx.row_entry, out[:, 8:8 + H * vdim], H, M, window, keep, scale,
-                           softcap or 0.0, lam, norm, 0.7, 1e-5, n_splits, partial)
+        if mma:
+            o.mapped_attention_mma(qo, kp, vp, table, ctx.cu_q, ctx.ctx_before, out[:, 8:8 + H * vdim], 1, n, H, M, window, keep,
+                                   scale, softcap or 0.0, lam, norm, 0.7, 1e-5)
+        else:
+            o.mapped_attention(qo, kp, vp, table, ctx.positions, ctx.row_entry, out[:, 8:8 + H * vdim], H, M, window, keep, scale,
+                               softcap or 0.0, lam, norm, 0.7, 1e-5, n_splits, partial)
         assert bool((out[:, :8] == 9).all()) and bool((out[:, 8 + H * vdim:] == 9).all())
         got.append(out[:, 8:8 + H * vdim].float().clone())
     return torch.cat(got)
@@ -182,8 +186,8 @@ def _run_core(dtype, q, k, v, window, keep, softcap, ps, scale, lam, norm, cuts,
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,H,G,dim,vdim,window,keep,softcap", [
-    (2, 4, 2, 16, 24, 37, 5, 6.0), (1, 3, 1, 24, 8, 20, 0, None), (2, 2, 2, 48, 96, 40, 4, 20.0), (1, 2, 1, 10, 5, 9, 12, None),
-    (2, 1, 1, 64, 64, None, 0, 3.0), (1, 8, 8, 64, 64, 96, 0, None), (2, 2, 1, 12, 200, 1, 1, None)])
+    (2, 4, 2, 16, 24, 37, 5, 6.0), (1, 3, 1, 24, 8, 20, 0, None), (2, 2, 2, 32, 80, 44, 6, 15.0), (1, 2, 1, 10, 5, 9, 12, None),
+    (2, 1, 1, 64, 64, None, 0, 3.0), (1, 6, 3, 64, 32, 80, 0, None), (2, 2, 1, 12, 200, 1, 1, None)])
 def test_attention_core_at_every_edge(dtype, M, H, G, dim, vdim, window, keep, softcap):
     """Keys that stand out just inside and just outside the window and the kept first tokens, at page borders, far
     back; as a whole prompt, in portions cut across those edges, and token by token with the keys cut into runs."""
@@ -215,6 +219,40 @@ def test_attention_core_at_every_edge(dtype, M, H, G, dim, vdim, window, keep, s
     assert rel_err(got, want) < tol
     if dtype == torch.float32:                                # runs and cuts change the order of the sums only
         assert rel_err(got, whole) < 1e-5
+    elif ops().mapped_attention_mma_takes(dim, vdim, dtype):  # the tensor-core kernel: whole, cut, and single rows
+        for c in ([(0, T)], cuts, [(0, T - 20)] + [(i, 1) for i in range(T - 20, T)]):
+            got = _run_core(dtype, q, k, v, window, keep, softcap, ps, scale, lam, M == 2, c, mma=True)
+            assert rel_err(got, want) < tol
+            assert rel_err(got, whole) < 1.5e-2               # both round the output to bfloat16, nothing else differs
+
+
+def test_tensor_core_kernel_with_several_entries_in_a_step():
+    """Entries of unequal length (one of a single token, one shorter than a tile, one of several tiles), each after
+    a context of its own, in one launch; each compared with the row-by-row kernel."""
+    dtype, H, G, M, dim, vdim, ps, window, keep = torch.bfloat16, 4, 2, 2, 32, 48, 8, 50, 3
+    o = ops()
+    lens, befores = [1, 9, 150, 70], [130, 0, 41, 64]
+    total = [a + b for a, b in zip(lens, befores)]
+    n_pages = sum(-(-t // ps) for t in total)
+    kp = torch.randn(n_pages, G * M, ps, dim, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, G, ps, vdim, device=DEV).to(dtype)
+    table = torch.full((4, 32), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    at = 0
+    for e, t in enumerate(total):
+        k = -(-t // ps)
+        table[e, :k] = perm[at:at + k]
+        at += k
+    table = table.to(DEV)
+    ctx = make_ctx(lens, befores, [0, 1, 2, 3], dtype=dtype)
+    n = sum(lens)
+    q = (2 * torch.randn(n, H * M * dim, device=DEV)).to(dtype)
+    a = torch.empty(n, H * vdim, dtype=dtype, device=DEV)
+    b = torch.empty_like(a)
+    o.mapped_attention(q, kp, vp, table, ctx.positions, ctx.row_entry, a, H, M, window, keep, 0.3, 7.0, 0.4, True, 0.6, 1e-5)
+    o.mapped_attention_mma(q, kp, vp, table, ctx.cu_q, ctx.ctx_before, b, 4, max(lens), H, M, window, keep, 0.3, 7.0, 0.4, True,
+                           0.6, 1e-5)
+    assert rel_err(b, a) < 1.5e-2
 
 
 def _mixer(spec, dtype, seed=0, owns_cache=True):
