@@ -52,7 +52,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
     const T* in = qkv + (size_t)row * ld;
     T* qo = q_out + (size_t)row * nQ * d;
     if (entry < 0) {                                   // padding row: defined output, no cache write
-        for (int j = threadIdx.x; j < nQ * d; j += MA_THREADS) ng_st(qo + j, 0.f);
+        for (int j = blockIdx.y * MA_THREADS + threadIdx.x; j < nQ * d; j += MA_THREADS * gridDim.y) ng_st(qo + j, 0.f);
         return;
     }
     size_t k_base = 0, v_base = 0;
@@ -60,13 +60,14 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
     if (nK + nV > 0) {
         const int page = table[(size_t)entry * table_stride + pos / page_size];
         page_ok = page >= 0 && page < num_pages;
-        if (!page_ok && threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
+        if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
         const size_t p = page_ok ? page : 0, slot = pos % page_size;
         k_base = (p * nK * page_size + slot) * d;
         v_base = (p * nV * page_size + slot) * dv;
     }
     const int half = d / 2;
-    for (int hh = warp; hh < nQ + nK; hh += MA_WARPS) {
+    // few rows: the heads are dealt over gridDim.y blocks of a row; many rows: one block walks all heads of its row
+    for (int hh = blockIdx.y * MA_WARPS + warp; hh < nQ + nK; hh += MA_WARPS * gridDim.y) {
         const bool is_q = hh < nQ;
         if (!is_q && !page_ok) continue;
         const T* src = in + (size_t)hh * d;
@@ -113,7 +114,7 @@ qkv_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* _
     }
     if (page_ok) {
         const T* vs = in + (size_t)(nQ + nK) * d;
-        for (int j = threadIdx.x; j < nV * dv; j += MA_THREADS) {
+        for (int j = blockIdx.y * MA_THREADS + threadIdx.x; j < nV * dv; j += MA_THREADS * gridDim.y) {
             const int hv = j / dv, c = j - hv * dv;
             v_pages[v_base + (size_t)hv * page_size * dv + c] = vs[j];
         }
@@ -129,12 +130,14 @@ NG_EXPORT int ng_qkv_prep(const void* qkv, void* q_out, const float* qw, const f
         rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && !inv_freq))
         return NG_BAD_SIZE;
     const size_t smem = (size_t)rot_dims * sizeof(float);
+    const int head_blocks = n_rows >= 256 ? 1 : min(64, (nQ + nK + MA_WARPS - 1) / MA_WARPS);
+    const dim3 grid(n_rows, head_blocks);
     if (act_bf16)
-        NG_LAUNCH((qkv_prep_kernel<__nv_bfloat16>), n_rows, MA_THREADS, smem, stream, (const __nv_bfloat16*)qkv,
+        NG_LAUNCH((qkv_prep_kernel<__nv_bfloat16>), grid, MA_THREADS, smem, stream, (const __nv_bfloat16*)qkv,
                   (__nv_bfloat16*)q_out, qw, kw, inv_freq, rot_dims, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, table,
                   table_stride, positions, row_entry, nQ, nK, nV, d, dv, page_size, num_pages, eps, status);
     else
-        NG_LAUNCH((qkv_prep_kernel<float>), n_rows, MA_THREADS, smem, stream, (const float*)qkv, (float*)q_out, qw, kw,
+        NG_LAUNCH((qkv_prep_kernel<float>), grid, MA_THREADS, smem, stream, (const float*)qkv, (float*)q_out, qw, kw,
                   inv_freq, rot_dims, (float*)k_pages, (float*)v_pages, table, table_stride, positions, row_entry, nQ, nK, nV,
                   d, dv, page_size, num_pages, eps, status);
     return ng_launch_status();
@@ -148,18 +151,23 @@ struct MaParams {
     float scale, softcap, lambda, post_scale, eps; int head_norm;
 };
 
+// the two bfloat16 values of a 32-bit word as float32: a bfloat16 is the upper half of a float32, so a shift and a
+// mask do it on the integer units (no conversion instruction)
+__device__ __forceinline__ float ma_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float ma_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
 // dot of a key's row with q (shared memory, float32): 16-byte pieces when the row allows it
 __device__ __forceinline__ float ma_dot(const __nv_bfloat16* k, const float* q, int d, bool vec) {
     float s = 0.f;
     if (vec) {
+#pragma unroll 4
         for (int c = 0; c < d; c += 8) {
             const uint4 u = *reinterpret_cast<const uint4*>(k + c);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                s = fmaf(q[c + 2 * e], __low2float(h[e]), s);
-                s = fmaf(q[c + 2 * e + 1], __high2float(h[e]), s);
-            }
+            const float4 qa = *reinterpret_cast<const float4*>(q + c), qb = *reinterpret_cast<const float4*>(q + c + 4);
+            s = fmaf(qa.x, ma_lo(u.x), s); s = fmaf(qa.y, ma_hi(u.x), s);
+            s = fmaf(qa.z, ma_lo(u.y), s); s = fmaf(qa.w, ma_hi(u.y), s);
+            s = fmaf(qb.x, ma_lo(u.z), s); s = fmaf(qb.y, ma_hi(u.z), s);
+            s = fmaf(qb.z, ma_lo(u.w), s); s = fmaf(qb.w, ma_hi(u.w), s);
         }
     } else {
         for (int c = 0; c < d; ++c) s = fmaf(q[c], __bfloat162float(k[c]), s);
@@ -169,9 +177,10 @@ __device__ __forceinline__ float ma_dot(const __nv_bfloat16* k, const float* q, 
 __device__ __forceinline__ float ma_dot(const float* k, const float* q, int d, bool vec) {
     float s = 0.f;
     if (vec) {
+#pragma unroll 4
         for (int c = 0; c < d; c += 4) {
-            const float4 u = *reinterpret_cast<const float4*>(k + c);
-            s = fmaf(q[c], u.x, s); s = fmaf(q[c + 1], u.y, s); s = fmaf(q[c + 2], u.z, s); s = fmaf(q[c + 3], u.w, s);
+            const float4 u = *reinterpret_cast<const float4*>(k + c), qa = *reinterpret_cast<const float4*>(q + c);
+            s = fmaf(qa.x, u.x, s); s = fmaf(qa.y, u.y, s); s = fmaf(qa.z, u.z, s); s = fmaf(qa.w, u.w, s);
         }
     } else {
         for (int c = 0; c < d; ++c) s = fmaf(q[c], k[c], s);
@@ -179,7 +188,10 @@ __device__ __forceinline__ float ma_dot(const float* k, const float* q, int d, b
     return s;
 }
 __device__ __forceinline__ float2 ma_ld_pair(const __nv_bfloat16* v, int c, int dv, bool vec) {
-    if (vec) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(v + c));
+    if (vec) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(v + c);
+        return make_float2(ma_lo(w), ma_hi(w));
+    }
     return make_float2(c < dv ? __bfloat162float(v[c]) : 0.f, c + 1 < dv ? __bfloat162float(v[c + 1]) : 0.f);
 }
 __device__ __forceinline__ float2 ma_ld_pair(const float* v, int c, int dv, bool vec) {
@@ -210,14 +222,16 @@ __device__ __forceinline__ void ma_finish(const MaParams& p, T* o, const float* 
     for (int c = threadIdx.x; c < p.dv; c += MA_THREADS, ++n) ng_st(o + c, keep[n] * r);
 }
 
-template <typename T, int M>
+// DVU: pairs of value columns a lane holds (dv <= 64 * DVU): registers and work follow the head's real size
+template <typename T, int M, int DVU>
 __global__ void __launch_bounds__(MA_THREADS)
 mapped_attention_kernel(const MaParams p) {
     extern __shared__ float sm[];
     __shared__ float red[32];
     __shared__ float st_m[MA_WARPS][M], st_l[MA_WARPS][M], fin_l[M];
-    float* q_s = sm;                                    // [M][d]
-    float* acc_s = sm + M * p.d;                        // [MA_WARPS][M][dv], later [M][dv] merged in place of warp 0
+    float* q_s = sm;                                    // [M][d4], d4 = d rounded up to 4: every map 16-byte aligned
+    const int d4 = (p.d + 3) & ~3;
+    float* acc_s = sm + M * d4;                        // [MA_WARPS][M][dv], later [M][dv] merged in place of warp 0
     ng_pdl_trigger();
     const int row = blockIdx.x, head = blockIdx.y, split = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -233,7 +247,7 @@ mapped_attention_kernel(const MaParams p) {
         return;
     }
     const T* q = reinterpret_cast<const T*>(ng_after_wait(p.q)) + ((size_t)row * p.nH + head) * M * d;
-    for (int c = threadIdx.x; c < M * d; c += MA_THREADS) q_s[c] = ng_ld(q + c);
+    for (int c = threadIdx.x; c < M * d; c += MA_THREADS) q_s[(c / d) * d4 + (c % d)] = ng_ld(q + c);
     __syncthreads();
     const int g = head / (p.nH / p.nG);
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
@@ -250,12 +264,12 @@ mapped_attention_kernel(const MaParams p) {
     const int* trow = p.table + (size_t)entry * p.table_stride;
     const bool kvec = sizeof(T) == 2 ? (d % 8 == 0 && ((uintptr_t)kp & 15) == 0) : (d % 4 == 0 && ((uintptr_t)kp & 15) == 0);
     const bool vvec = (dv % 2 == 0) && ((uintptr_t)vp & (2 * sizeof(T) - 1)) == 0;
-    float m_run[M], l_run[M], acc[M][MA_DVU][2];
+    float m_run[M], l_run[M], acc[M][DVU][2];
 #pragma unroll
     for (int m = 0; m < M; ++m) {
         m_run[m] = -INFINITY; l_run[m] = 0.f;
 #pragma unroll
-        for (int u = 0; u < MA_DVU; ++u) acc[m][u][0] = acc[m][u][1] = 0.f;
+        for (int u = 0; u < DVU; ++u) acc[m][u][0] = acc[m][u][1] = 0.f;
     }
     for (int tb = t0 + warp * 32; tb < t1; tb += MA_TILE) {
         const int t = tb + lane;
@@ -271,7 +285,7 @@ mapped_attention_kernel(const MaParams p) {
             const size_t kbase = ((pg * p.nG * M + g * M + m) * p.page_size + slot) * d;
             float s = -INFINITY;
             if (ok) {
-                s = ma_dot(kp + kbase, q_s + m * d, d, kvec) * p.scale;
+                s = ma_dot(kp + kbase, q_s + m * d4, d, kvec) * p.scale;
                 if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
             }
             const float m_new = fmaxf(m_run[m], ng_warp_max(s));
@@ -280,26 +294,34 @@ mapped_attention_kernel(const MaParams p) {
             l_run[m] = l_run[m] * corr + ng_warp_sum(pr[m]);
             m_run[m] = m_new;
 #pragma unroll
-            for (int u = 0; u < MA_DVU; ++u) { acc[m][u][0] *= corr; acc[m][u][1] *= corr; }
+            for (int u = 0; u < DVU; ++u) { acc[m][u][0] *= corr; acc[m][u][1] *= corr; }
         }
+        // eight keys at a time, their values requested before the first is used; a lane beyond the run's end has the
+        // weight 0 and the address of a key that is there (the row's own), so nothing is skipped inside a group
         const int cnt = min(32, t1 - tb);
-        for (int j = 0; j < cnt; ++j) {
-            const size_t vb = __shfl_sync(0xffffffffu, vbase, j);
-            float pj[M];
+        for (int j0 = 0; j0 < cnt; j0 += 8) {
+            float2 vv[8][DVU];
+            float pj[8][M];
 #pragma unroll
-            for (int m = 0; m < M; ++m) pj[m] = __shfl_sync(0xffffffffu, pr[m], j);
+            for (int jj = 0; jj < 8; ++jj) {
+                const size_t vb = __shfl_sync(0xffffffffu, vbase, j0 + jj);
 #pragma unroll
-            for (int u = 0; u < MA_DVU; ++u) {
-                const int c = 2 * lane + 64 * u;
-                if (c < dv) {
-                    const float2 v = ma_ld_pair(vp + vb, c, dv, vvec);
+                for (int m = 0; m < M; ++m) pj[jj][m] = __shfl_sync(0xffffffffu, pr[m], j0 + jj);
 #pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        acc[m][u][0] = fmaf(pj[m], v.x, acc[m][u][0]);
-                        acc[m][u][1] = fmaf(pj[m], v.y, acc[m][u][1]);
-                    }
+                for (int u = 0; u < DVU; ++u) {
+                    const int c = 2 * lane + 64 * u;
+                    vv[jj][u] = c < dv ? ma_ld_pair(vp + vb, c, dv, vvec) : make_float2(0.f, 0.f);
                 }
             }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+#pragma unroll
+                for (int u = 0; u < DVU; ++u)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        acc[m][u][0] = fmaf(pj[jj][m], vv[jj][u].x, acc[m][u][0]);
+                        acc[m][u][1] = fmaf(pj[jj][m], vv[jj][u].y, acc[m][u][1]);
+                    }
         }
     }
     // the warps' states, merged in warp order
@@ -307,7 +329,7 @@ mapped_attention_kernel(const MaParams p) {
     for (int m = 0; m < M; ++m) {
         if (lane == 0) { st_m[warp][m] = m_run[m]; st_l[warp][m] = l_run[m]; }
 #pragma unroll
-        for (int u = 0; u < MA_DVU; ++u) {
+        for (int u = 0; u < DVU; ++u) {
             const int c = 2 * lane + 64 * u;
             if (c < dv) acc_s[((size_t)warp * M + m) * dv + c] = acc[m][u][0];
             if (c + 1 < dv) acc_s[((size_t)warp * M + m) * dv + c + 1] = acc[m][u][1];
@@ -328,7 +350,7 @@ mapped_attention_kernel(const MaParams p) {
         }
         if (threadIdx.x == 0) fin_l[m] = lt;
     }
-    float merged[M][(2 * MA_DVU * 32 + MA_THREADS - 1) / MA_THREADS];
+    float merged[M][(2 * DVU * 32 + MA_THREADS - 1) / MA_THREADS];
     {
         int n = 0;
         for (int c = threadIdx.x; c < dv; c += MA_THREADS, ++n)
@@ -409,10 +431,12 @@ mapped_attention_merge_kernel(const MaParams p) {
 
 template <typename T, int M>
 static int ma_launch(const MaParams& p, int n_rows, cudaStream_t stream) {
-    const size_t smem = ((size_t)M * p.d + (size_t)MA_WARPS * M * p.dv) * sizeof(float);
+    const size_t smem = ((size_t)M * ((p.d + 3) & ~3) + (size_t)MA_WARPS * M * p.dv) * sizeof(float);
     if (smem > 48 * 1024) return NG_BAD_SIZE;
     dim3 grid(n_rows, p.nH, p.n_splits);
-    NG_LAUNCH((mapped_attention_kernel<T, M>), grid, MA_THREADS, smem, stream, p);
+    if (p.dv <= 64) NG_LAUNCH((mapped_attention_kernel<T, M, 1>), grid, MA_THREADS, smem, stream, p);
+    else if (p.dv <= 128) NG_LAUNCH((mapped_attention_kernel<T, M, 2>), grid, MA_THREADS, smem, stream, p);
+    else NG_LAUNCH((mapped_attention_kernel<T, M, 4>), grid, MA_THREADS, smem, stream, p);
     if (p.n_splits > 1) {
         dim3 g2(n_rows, p.nH);
         NG_LAUNCH((mapped_attention_merge_kernel<T, M>), g2, MA_THREADS, (size_t)M * p.dv * sizeof(float), stream, p);

@@ -8,7 +8,7 @@
 // A block takes consecutive rows of one entry and one query head: 64 rows (one map) or 32 rows (two maps; a warp
 // per map and 16 rows, the maps combined in the epilogue), and walks the keys the block's rows can see, kept first
 // tokens then the window, in tiles of 64: keys (of each map) and values are staged once in shared memory for the four
-// warps (16-byte copies, page by page through the block table), S = Q K^T in registers, mask and cap per element,
+// warps (16-byte asynchronous copies through the block table, a tile ahead of the one being worked on), S = Q K^T in registers, mask and cap per element,
 // P V with P straight from the accumulators' layout, values through ldmatrix.trans.  Specialised on the key and
 // value sizes (-DNG_MA_D, -DNG_MA_DV: multiples of 16, up to 128).
 #include "ng_common.cuh"
@@ -46,6 +46,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 16 bytes from global to shared memory without passing registers; `real` false: zeros instead (nothing is read)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool real) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(n) : "memory");
+}
 __device__ __forceinline__ uint32_t pack2(float x, float y) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -66,11 +72,11 @@ mapped_attention_mma_kernel(const MmaParams p) {
     constexpr int ROWS = (WARPS / M) * 16;               // rows of a block
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                        // [M][ROWS][QP]
-    bf16* Ks = Qs + M * ROWS * QP;                                       // [M][KT][KP]
-    bf16* Vs = Ks + M * KT * KP;                                         // [KT][VP]
+    bf16* Ks = Qs + M * ROWS * QP;                                       // [2][M][KT][KP]
+    bf16* Vs = Ks + 2 * M * KT * KP;                                     // [2][KT][VP]
     float* Os = reinterpret_cast<float*>(Ks);                            // epilogue: [M][ROWS][DV], over the tiles
-    __shared__ int kpos_s[KT];
-    __shared__ long long koff_s[KT];                                     // element offset of the key's page slot, -1: none
+    __shared__ int kpos_s[3][KT];                                        // per tile in flight or in use (three: see the loop)
+    __shared__ long long koff_s[3][KT];                                  // element offset of the key's page slot, -1: none
     ng_pdl_trigger();
     const int entry = blockIdx.y, head = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -113,8 +119,9 @@ mapped_attention_mma_kernel(const MmaParams p) {
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     const int* trow = p.table + (size_t)entry * p.table_stride;
 
-    for (int t0 = 0; t0 < n_keys; t0 += KT) {
-        __syncthreads();                                 // the tile before is done with
+    // Two buffers: while the warps work on a tile, the next one is on its way (cp.async, 16 bytes a copy; a key that
+    // is not there is filled with zeros).  A tile's page slots are looked up one iteration ahead of its copies.
+    auto lookup = [&](int t0, int b) {
         if (tid < KT) {
             const int t = t0 + tid;
             int kpos = -1;
@@ -125,31 +132,43 @@ mapped_attention_mma_kernel(const MmaParams p) {
                 if (page >= 0 && page < p.num_pages) off = (long long)page * p.page_size + (kpos % p.page_size);
                 else kpos = -1;
             }
-            kpos_s[tid] = kpos;
-            koff_s[tid] = off;
+            kpos_s[b][tid] = kpos;
+            koff_s[b][tid] = off;
         }
-        __syncthreads();
+    };
+    auto copy_tile = [&](int b, int mb) {
+        bf16* kb = Ks + (size_t)b * M * KT * KP;
+        bf16* vb = Vs + (size_t)b * KT * VP;
         for (int i = tid; i < M * KT * (D / 8); i += THREADS) {
             const int ch = i % (D / 8), key = (i / (D / 8)) % KT, m = i / ((D / 8) * KT);
-            const long long off = koff_s[key];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (off >= 0) {
-                const long long page = off / p.page_size, slot = off % p.page_size;
-                v = *reinterpret_cast<const uint4*>(p.k_pages + (((size_t)page * p.nG * M + (size_t)g * M + m) * p.page_size + slot) * D + ch * 8);
-            }
-            *reinterpret_cast<uint4*>(Ks + ((size_t)m * KT + key) * KP + ch * 8) = v;
+            const long long off = koff_s[mb][key];
+            const long long page = off >= 0 ? off / p.page_size : 0, slot = off >= 0 ? off % p.page_size : 0;
+            cp_async16(kb + ((size_t)m * KT + key) * KP + ch * 8,
+                       p.k_pages + (((size_t)page * p.nG * M + (size_t)g * M + m) * p.page_size + slot) * D + ch * 8, off >= 0);
         }
         for (int i = tid; i < KT * (DV / 8); i += THREADS) {
             const int ch = i % (DV / 8), key = i / (DV / 8);
-            const long long off = koff_s[key];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (off >= 0) {
-                const long long page = off / p.page_size, slot = off % p.page_size;
-                v = *reinterpret_cast<const uint4*>(p.v_pages + (((size_t)page * p.nG + g) * p.page_size + slot) * DV + ch * 8);
-            }
-            *reinterpret_cast<uint4*>(Vs + (size_t)key * VP + ch * 8) = v;
+            const long long off = koff_s[mb][key];
+            const long long page = off >= 0 ? off / p.page_size : 0, slot = off >= 0 ? off % p.page_size : 0;
+            cp_async16(vb + (size_t)key * VP + ch * 8,
+                       p.v_pages + (((size_t)page * p.nG + g) * p.page_size + slot) * DV + ch * 8, off >= 0);
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    lookup(0, 0);
+    __syncthreads();
+    copy_tile(0, 0);
+    int buf = 0, it = 0;
+    for (int t0 = 0; t0 < n_keys; t0 += KT, buf ^= 1, ++it) {
+        const bool more = t0 + KT < n_keys;
+        // the lookup of tile it+1 goes to slot (it+1) % 3: slower warps may still read tile it-1's positions (slot
+        // (it-1) % 3) and tile it's copies were made from slot it % 3; the slot's last readers (tile it-2) passed the
+        // barrier of the iteration before
+        if (more) lookup(t0 + KT, (it + 1) % 3);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                 // this tile has landed; the other data buffer is free
+        if (more) copy_tile(buf ^ 1, (it + 1) % 3);
+        const int* kpos_t = kpos_s[it % 3];
         // does any row of the warp see any key of the tile?  (positions ascend within both parts of the list)
         bool any = warp_live;
         if (any) {
@@ -165,7 +184,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
         float s[KT / 8][4];
 #pragma unroll
         for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-        const bf16* kt = Ks + (size_t)map * KT * KP;
+        const bf16* kt = Ks + ((size_t)buf * M + map) * KT * KP;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
 #pragma unroll
@@ -182,7 +201,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
         for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int kpos = kpos_s[j * 8 + 2 * tq + (e & 1)];
+                const int kpos = kpos_t[j * 8 + 2 * tq + (e & 1)];
                 const int pos = (e < 2) ? pos_a : pos_b;
                 const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
                 const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
@@ -222,7 +241,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
 #pragma unroll
             for (int np = 0; np < DV / 16; ++np) {
                 uint32_t b[4];
-                ldsm_x4_t(b, Vs + ((size_t)kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + np * 16 + (lane >> 4) * 8);
+                ldsm_x4_t(b, Vs + (size_t)buf * KT * VP + ((size_t)kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + np * 16 + (lane >> 4) * 8);
                 mma_bf16(o[2 * np], al, b[0], b[1]);
                 mma_bf16(o[2 * np + 1], al, b[2], b[3]);
                 mma_bf16(o[2 * np], am, b[0], b[1]);
@@ -274,7 +293,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
 template <int M>
 static int mma_launch(const MmaParams& p, int n_entries, int max_q, cudaStream_t stream) {
     constexpr int ROWS = (WARPS / M) * 16;
-    const size_t tiles = ((size_t)M * ROWS * QP + (size_t)M * KT * KP + (size_t)KT * VP) * sizeof(bf16);
+    const size_t tiles = ((size_t)M * ROWS * QP + 2 * ((size_t)M * KT * KP + (size_t)KT * VP)) * sizeof(bf16);
     const size_t epi = (size_t)M * ROWS * QP * sizeof(bf16) + (size_t)M * ROWS * DV * sizeof(float);
     const size_t smem = tiles > epi ? tiles : epi;
     static bool attr = false;

@@ -29,7 +29,7 @@ class MappedAttention:
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
     SPLIT_MAX_ROWS = 32    # steps of up to this many rows may cut each row's keys into runs
-    SPLIT_MIN_KEYS = 256   # ... of at least this many keys
+    SPLIT_MIN_KEYS = 128   # ... of at least this many keys (one tile of the kernel)
     MAX_SPLITS = 16
 
     def __init__(self, spec, *, dtype, device, owns_cache=True):
@@ -112,7 +112,7 @@ class MappedAttention:
         most = min(self.MAX_SPLITS, longest // self.SPLIT_MIN_KEYS)
         if most <= 1:
             return 1
-        return max(1, min(most, -(-2 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))))
+        return max(1, min(most, -(-6 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))))
 
     def core(self, x, ctx, cache, out):
         """out[N, n_heads * value_dim] (may be a block of columns of a wider buffer): the heads' outputs."""
