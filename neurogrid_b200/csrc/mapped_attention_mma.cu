@@ -1,6 +1,6 @@
 // The attention of mapped_attention.cu for long bfloat16 steps, on the tensor cores (mma.sync m16n8k16).
 //
-// Same mathematics: float32 scores, float32 online softmax, float32 weights.  The products run on the tensor cores
+// Same mathematics: float32 scores, float32 online softmax (as powers of two, on the special-function unit), float32 weights.  The products run on the tensor cores
 // without giving that up: q and k are bfloat16 as the cache holds them, so q.k is a float32 sum of exact products;
 // a float32 weight p enters the weighted sum as three bfloat16 terms hi + mid + lo (what is left is below 2^-24 p),
 // each term's products with the bfloat16 values exact in the float32 accumulators.
@@ -52,6 +52,16 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool real
     const int n = real ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(d), "l"(src), "r"(n) : "memory");
 }
+// 2^x on the special-function unit (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// tanh(x) = 1 - 2 / (1 + e^(2x)): exact limits at both ends, absolute error of a few 1e-7
+__device__ __forceinline__ float tanh_ex2(float x) {
+    return 1.f - __fdividef(2.f, 1.f + ex2f(x * 2.8853900817779268f));
+}
 __device__ __forceinline__ uint32_t pack2(float x, float y) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -67,7 +77,7 @@ __device__ __forceinline__ void split3(float x, float y, uint32_t& hi, uint32_t&
 }
 
 template <int M>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 mapped_attention_mma_kernel(const MmaParams p) {
     constexpr int ROWS = (WARPS / M) * 16;               // rows of a block
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -76,7 +86,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
     bf16* Vs = Ks + 2 * M * KT * KP;                                     // [2][KT][VP]
     float* Os = reinterpret_cast<float*>(Ks);                            // epilogue: [M][ROWS][DV], over the tiles
     __shared__ int kpos_s[3][KT];                                        // per tile in flight or in use (three: see the loop)
-    __shared__ long long koff_s[3][KT];                                  // element offset of the key's page slot, -1: none
+    __shared__ long long koff_s[3][KT];
+    __shared__ int tile_bad_s[3][2];                                     // a key of the tile has no page                                  // element offset of the key's page slot, -1: none
     ng_pdl_trigger();
     const int entry = blockIdx.y, head = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -134,6 +145,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
             }
             kpos_s[b][tid] = kpos;
             koff_s[b][tid] = off;
+            const unsigned bad = __ballot_sync(0xffffffffu, t < n_keys && off < 0);      // KT = 64: warps 0 and 1, whole
+            if (lane == 0) tile_bad_s[b][warp] = bad != 0u;
         }
     };
     auto copy_tile = [&](int b, int mb) {
@@ -195,19 +208,30 @@ mapped_attention_mma_kernel(const MmaParams p) {
                 mma_bf16(s[2 * jp + 1], qf[ks], b[2], b[3]);
             }
         }
-        // ---- scale, cap, mask; online softmax in float32
+        // ---- scale, cap, mask; online softmax in float32, in powers of two (scores times log2 e)
+        // a tile that every row of the warp sees whole (the bulk of a long window) needs no mask
+        bool interior;
+        {
+            const int k_first = t0 < n_sink ? t0 : lo + (t0 - n_sink), k_last = k_first + KT - 1;
+            interior = t0 + KT <= n_keys && (t0 >= n_sink || t0 + KT <= n_sink) && wt * 16 + 15 < n_rows &&
+                       k_last <= w_first && (p.window <= 0 || w_first + 15 - k_first < p.window || k_last < p.keep_first) &&
+                       !tile_bad_s[it % 3][0] && !tile_bad_s[it % 3][1];
+        }
+        constexpr float LOG2E = 1.4426950408889634f;
+        const float sc2 = p.scale * LOG2E, inv_cap = p.softcap > 0.f ? p.scale / p.softcap : 0.f, cap2 = p.softcap * LOG2E;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
         for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int kpos = kpos_t[j * 8 + 2 * tq + (e & 1)];
-                const int pos = (e < 2) ? pos_a : pos_b;
-                const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
-                const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
-                float v = s[j][e] * p.scale;
-                if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
-                v = vis ? v : -INFINITY;
+                float v = p.softcap > 0.f ? cap2 * tanh_ex2(s[j][e] * inv_cap) : s[j][e] * sc2;
+                if (!interior) {
+                    const int kpos = kpos_t[j * 8 + 2 * tq + (e & 1)];
+                    const int pos = (e < 2) ? pos_a : pos_b;
+                    const bool row_ok = ((e < 2) ? row_a : row_b) < n_rows;
+                    const bool vis = row_ok && kpos >= 0 && kpos <= pos && (p.window <= 0 || pos - kpos < p.window || kpos < p.keep_first);
+                    v = vis ? v : -INFINITY;
+                }
                 s[j][e] = v;
                 if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
             }
@@ -217,7 +241,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
         const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float ca = m_a == -INFINITY ? 0.f : expf(m_a - mn_a), cb = m_b == -INFINITY ? 0.f : expf(m_b - mn_b);
+        const float ca = m_a == -INFINITY ? 0.f : ex2f(m_a - mn_a), cb = m_b == -INFINITY ? 0.f : ex2f(m_b - mn_b);
         const float ua = mn_a == -INFINITY ? 0.f : mn_a, ub = mn_b == -INFINITY ? 0.f : mn_b;
         m_a = mn_a; m_b = mn_b;
         l_a *= ca; l_b *= cb;
@@ -225,8 +249,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
         for (int j = 0; j < DV / 8; ++j) { o[j][0] *= ca; o[j][1] *= ca; o[j][2] *= cb; o[j][3] *= cb; }
 #pragma unroll
         for (int j = 0; j < KT / 8; ++j) {
-            s[j][0] = expf(s[j][0] - ua); s[j][1] = expf(s[j][1] - ua);        // exp(-inf) = 0 for what the mask hides
-            s[j][2] = expf(s[j][2] - ub); s[j][3] = expf(s[j][3] - ub);
+            s[j][0] = ex2f(s[j][0] - ua); s[j][1] = ex2f(s[j][1] - ua);        // 2^-inf = 0 for what the mask hides
+            s[j][2] = ex2f(s[j][2] - ub); s[j][3] = ex2f(s[j][3] - ub);
             l_a += s[j][0] + s[j][1];
             l_b += s[j][2] + s[j][3];
         }
@@ -242,7 +266,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
             for (int np = 0; np < DV / 16; ++np) {
                 uint32_t b[4];
                 ldsm_x4_t(b, Vs + (size_t)buf * KT * VP + ((size_t)kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + np * 16 + (lane >> 4) * 8);
-                mma_bf16(o[2 * np], al, b[0], b[1]);
+                mma_bf16(o[2 * np], al, b[0], b[1]);        // smallest terms first
                 mma_bf16(o[2 * np + 1], al, b[2], b[3]);
                 mma_bf16(o[2 * np], am, b[0], b[1]);
                 mma_bf16(o[2 * np + 1], am, b[2], b[3]);
