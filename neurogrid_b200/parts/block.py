@@ -204,6 +204,9 @@ class ParallelBlock:
                 b = b if b2 is None else (b2 if b is None else b + b2)
             self.w_out, self.b_out = w, b
             self.b_out_f32 = b.to(torch.float32).contiguous() if b is not None else None
+            for part in (self.mixer, self.ffn):              # the stacked matrix serves; the parts' own copies go
+                if part is not None and self.ffn is not None and hasattr(part, "drop_out_weight"):
+                    part.drop_out_weight()
 
     def cache_need(self):
         return self.mixer.cache_need()

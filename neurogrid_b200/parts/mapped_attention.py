@@ -101,6 +101,10 @@ class MappedAttention:
     def out_weight(self):
         return self.w_o, self.b_o
 
+    def drop_out_weight(self):
+        """The caller keeps a stacked copy of the output matrix and will not call ``forward``."""
+        self.w_o = None
+
     def _splits(self, n_rows, cache):
         """Runs a row's keys are cut into: from the step's rows and the layer's constants only (a graph's launches)."""
         s = self.spec

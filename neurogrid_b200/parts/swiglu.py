@@ -51,6 +51,10 @@ class SwiGLU:
     def out_weight(self):
         return self.w_down, None
 
+    def drop_out_weight(self):
+        """The caller keeps a stacked copy of the output matrix and will not call ``forward``."""
+        self.w_down = None
+
     def gated(self, x, ctx, act):
         """act[N, intermediate] (may be a block of columns of a wider buffer) = act(gate x) * (up x)."""
         s = self.spec
