@@ -462,3 +462,26 @@ NG_EXPORT int ng_mapped_attention(const void* q, const void* k_pages, const void
     if (act_bf16) return n_maps == 2 ? ma_launch<__nv_bfloat16, 2>(p, n_rows, stream) : ma_launch<__nv_bfloat16, 1>(p, n_rows, stream);
     return n_maps == 2 ? ma_launch<float, 2>(p, n_rows, stream) : ma_launch<float, 1>(p, n_rows, stream);
 }
+
+// The runs' states of every (row, head) merged and the heads finished (maps combined, head norm), for states that another
+// kernel left in `partial` (float32 [n_rows, nH, n_splits, n_maps, dv + 2]: maximum, sum, weighted values).  Rows of no
+// entry get zeros.
+NG_EXPORT int ng_mapped_attention_merge(float* partial, const int* row_entry, void* out, int out_ld, int n_rows, int nH,
+                                        int n_maps, int dv, int n_splits, float lambda, float post_scale, float eps,
+                                        int head_norm, int act_bf16, cudaStream_t stream) {
+    if (n_rows <= 0) return NG_OK;
+    if (!partial || dv <= 0 || dv > 64 * MA_DVU || nH <= 0 || nH > 65535 || n_maps < 1 || n_maps > 2 || n_splits < 1 || out_ld < nH * dv)
+        return NG_BAD_SIZE;
+    MaParams p{nullptr, nullptr, nullptr, nullptr, 0, nullptr, row_entry, out, out_ld, partial, nH, 1, 0, dv, 1, 0, 0, 0, n_splits,
+               0.f, 0.f, lambda, post_scale, eps, head_norm};
+    dim3 grid(n_rows, nH);
+    const size_t smem = (size_t)n_maps * dv * sizeof(float);
+    if (act_bf16) {
+        if (n_maps == 2) NG_LAUNCH((mapped_attention_merge_kernel<__nv_bfloat16, 2>), grid, MA_THREADS, smem, stream, p);
+        else NG_LAUNCH((mapped_attention_merge_kernel<__nv_bfloat16, 1>), grid, MA_THREADS, smem, stream, p);
+    } else {
+        if (n_maps == 2) NG_LAUNCH((mapped_attention_merge_kernel<float, 2>), grid, MA_THREADS, smem, stream, p);
+        else NG_LAUNCH((mapped_attention_merge_kernel<float, 1>), grid, MA_THREADS, smem, stream, p);
+    }
+    return ng_launch_status();
+}

@@ -29,6 +29,7 @@ struct MmaParams {
     const int* cu_q; const int* ctx_before; bf16* out; int out_ld;
     int nH, nG, page_size, num_pages, window, keep_first;
     float scale, softcap, lambda, post_scale, eps; int head_norm;
+    float* partial; int n_splits;      // GROUP: runs of keys, their states [row, head, run, map, DV + 2]
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
@@ -76,7 +77,10 @@ __device__ __forceinline__ void split3(float x, float y, uint32_t& hi, uint32_t&
     lo = pack2(xr - xm, yr - ym);
 }
 
-template <int M>
+// GROUP: for entries that bring one token.  The rows of the tile are then the query heads of one KV group (up to 16; they
+// share keys and values and here also the position), a block takes (run of keys, entry, KV group), and instead of the
+// finished heads it leaves each run's state (maximum, sum, weighted values) for the kernel that merges runs.
+template <int M, bool GROUP>
 __global__ void __launch_bounds__(THREADS, 3)
 mapped_attention_mma_kernel(const MmaParams p) {
     constexpr int ROWS = (WARPS / M) * 16;               // rows of a block
@@ -89,15 +93,17 @@ mapped_attention_mma_kernel(const MmaParams p) {
     __shared__ long long koff_s[3][KT];
     __shared__ int tile_bad_s[3][2];                                     // a key of the tile has no page                                  // element offset of the key's page slot, -1: none
     ng_pdl_trigger();
-    const int entry = blockIdx.y, head = blockIdx.z;
+    const int entry = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q0 = p.cu_q[entry], q_len = p.cu_q[entry + 1] - q0;
-    const int r0 = blockIdx.x * ROWS;                    // first row of the block within the entry
+    const int r0 = GROUP ? 0 : blockIdx.x * ROWS;        // first row of the block within the entry
     ng_pdl_wait();
-    if (r0 >= q_len) return;
+    if (GROUP ? q_len != 1 : r0 >= q_len) return;
     const int before = p.ctx_before[entry];
-    const int n_rows = min(ROWS, q_len - r0);
-    const int g = head / (p.nH / p.nG);
+    const int group_heads = p.nH / p.nG;
+    const int n_rows = GROUP ? group_heads : min(ROWS, q_len - r0);
+    const int g = GROUP ? blockIdx.z : blockIdx.z / group_heads;
+    const int head = GROUP ? g * group_heads : blockIdx.z;               // GROUP: the first head of the tile's rows
     const int map = M == 2 ? (warp & 1) : 0;
     const int wt = M == 2 ? (warp >> 1) : warp;          // the warp's tile of 16 rows
     const bf16* qg = ng_after_wait(p.q);
@@ -106,7 +112,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
         const int ch = i % (D / 8), row = (i / (D / 8)) % ROWS, m = i / ((D / 8) * ROWS);
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (row < n_rows)
-            v = *reinterpret_cast<const uint4*>(qg + ((size_t)(q0 + r0 + row) * p.nH + head) * M * D + (size_t)m * D + ch * 8);
+            v = *reinterpret_cast<const uint4*>(qg + ((size_t)(q0 + (GROUP ? 0 : r0 + row)) * p.nH + head + (GROUP ? row : 0)) * M * D +
+                                                (size_t)m * D + ch * 8);
         *reinterpret_cast<uint4*>(Qs + ((size_t)m * ROWS + row) * QP + ch * 8) = v;
     }
     __syncthreads();
@@ -115,14 +122,22 @@ mapped_attention_mma_kernel(const MmaParams p) {
     for (int ks = 0; ks < D / 16; ++ks)
         ldsm_x4(qf[ks], Qs + ((size_t)map * ROWS + wt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QP + ks * 16 + (lane >> 4) * 8);
     // ---- the keys the block's rows see: kept first tokens [0, n_sink), then [lo, last position]
-    const int pos_first = before + r0, pos_last = before + r0 + n_rows - 1;
+    const int pos_first = before + r0, pos_last = GROUP ? pos_first : before + r0 + n_rows - 1;
     const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
     const int n_sink = min(p.keep_first, lo);
-    const int n_keys = n_sink + (pos_last - lo + 1);
+    const int all_keys = n_sink + (pos_last - lo + 1);
+    int t_begin = 0, n_keys = all_keys;                  // the block's run of the key list: [t_begin, n_keys)
+    if (GROUP && p.n_splits > 1) {
+        const int tiles = (all_keys + KT - 1) / KT, per = (tiles + p.n_splits - 1) / p.n_splits;
+        t_begin = min(all_keys, (int)blockIdx.x * per * KT);
+        n_keys = min(all_keys, t_begin + per * KT);
+    }
     const int gq = lane >> 2, tq = lane & 3;
     const int row_a = wt * 16 + gq, row_b = row_a + 8;   // this thread's two rows within the block
-    const int pos_a = pos_first + row_a, pos_b = pos_first + row_b;
-    const int w_first = pos_first + wt * 16, w_last = min(pos_last, w_first + 15);   // the warp's positions
+    const int pos_a = GROUP ? pos_first : pos_first + row_a, pos_b = GROUP ? pos_first : pos_first + row_b;
+    const int w_first = GROUP ? pos_first : pos_first + wt * 16;                     // the warp's positions
+    const int w_last = GROUP ? pos_first : min(pos_last, w_first + 15);
+    const int w_span = GROUP ? 0 : 15;
     const bool warp_live = wt * 16 < n_rows;
     float o[DV / 8][4];
 #pragma unroll
@@ -168,11 +183,11 @@ mapped_attention_mma_kernel(const MmaParams p) {
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    lookup(0, 0);
+    lookup(t_begin, 0);
     __syncthreads();
     copy_tile(0, 0);
     int buf = 0, it = 0;
-    for (int t0 = 0; t0 < n_keys; t0 += KT, buf ^= 1, ++it) {
+    for (int t0 = t_begin; t0 < n_keys; t0 += KT, buf ^= 1, ++it) {
         const bool more = t0 + KT < n_keys;
         // the lookup of tile it+1 goes to slot (it+1) % 3: slower warps may still read tile it-1's positions (slot
         // (it-1) % 3) and tile it's copies were made from slot it % 3; the slot's last readers (tile it-2) passed the
@@ -213,8 +228,8 @@ mapped_attention_mma_kernel(const MmaParams p) {
         bool interior;
         {
             const int k_first = t0 < n_sink ? t0 : lo + (t0 - n_sink), k_last = k_first + KT - 1;
-            interior = t0 + KT <= n_keys && (t0 >= n_sink || t0 + KT <= n_sink) && wt * 16 + 15 < n_rows &&
-                       k_last <= w_first && (p.window <= 0 || w_first + 15 - k_first < p.window || k_last < p.keep_first) &&
+            interior = t0 + KT <= n_keys && (t0 >= n_sink || t0 + KT <= n_sink) && (GROUP || wt * 16 + 15 < n_rows) &&
+                       k_last <= w_first && (p.window <= 0 || w_first + w_span - k_first < p.window || k_last < p.keep_first) &&
                        !tile_bad_s[it % 3][0] && !tile_bad_s[it % 3][1];
         }
         constexpr float LOG2E = 1.4426950408889634f;
@@ -276,11 +291,33 @@ mapped_attention_mma_kernel(const MmaParams p) {
         }
     }
     // ---- epilogue: each map's a = O / l into shared memory, then the maps combined row by row
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // (an empty run has copies in flight that nobody waited for)
     __syncthreads();                                     // every warp has left the tiles
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (GROUP) {
+        // the run's state per head and map, as the kernel that merges runs reads it: maximum (natural logarithm), sum,
+        // weighted values relative to that maximum
+        if (warp_live) {
+            constexpr float LN2 = 0.6931471805599453f;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = half ? row_b : row_a;
+                if (r < n_rows) {
+                    float* ps = p.partial + ((((size_t)q0 * p.nH + head + r) * p.n_splits + blockIdx.x) * M + map) * (DV + 2);
+                    if (tq == 0) { ps[0] = (half ? m_b : m_a) * LN2; ps[1] = half ? l_b : l_a; }
+#pragma unroll
+                    for (int j = 0; j < DV / 8; ++j) {
+                        ps[2 + j * 8 + 2 * tq] = o[j][2 * half];
+                        ps[2 + j * 8 + 2 * tq + 1] = o[j][2 * half + 1];
+                    }
+                }
+            }
+        }
+        return;
+    }
     const float ia = l_a > 0.f ? 1.f / l_a : 0.f, ib = l_b > 0.f ? 1.f / l_b : 0.f;
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j) {
@@ -314,7 +351,7 @@ mapped_attention_mma_kernel(const MmaParams p) {
     }
 }
 
-template <int M>
+template <int M, bool GROUP>
 static int mma_launch(const MmaParams& p, int n_entries, int max_q, cudaStream_t stream) {
     constexpr int ROWS = (WARPS / M) * 16;
     const size_t tiles = ((size_t)M * ROWS * QP + 2 * ((size_t)M * KT * KP + (size_t)KT * VP)) * sizeof(bf16);
@@ -322,13 +359,13 @@ static int mma_launch(const MmaParams& p, int n_entries, int max_q, cudaStream_t
     const size_t smem = tiles > epi ? tiles : epi;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(mapped_attention_mma_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(mapped_attention_mma_kernel<M, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         attr = true;
     }
-    dim3 grid((max_q + ROWS - 1) / ROWS, n_entries, p.nH);
+    dim3 grid(GROUP ? p.n_splits : (max_q + ROWS - 1) / ROWS, n_entries, GROUP ? p.nG : p.nH);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
-    NG_LAUNCH((mapped_attention_mma_kernel<M>), grid, THREADS, smem, stream, p);
+    NG_LAUNCH((mapped_attention_mma_kernel<M, GROUP>), grid, THREADS, smem, stream, p);
     return ng_launch_status();
 }
 
@@ -344,6 +381,26 @@ NG_EXPORT int ng_mapped_attention_mma(const void* q, const void* k_pages, const 
         window < 0 || keep_first < 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, (bf16*)out,
-                out_ld, nH, nG, page_size, num_pages, window, keep_first, scale, softcap, lambda, post_scale, eps, head_norm};
-    return n_maps == 2 ? mma_launch<2>(p, n_entries, max_q, stream) : mma_launch<1>(p, n_entries, max_q, stream);
+                out_ld, nH, nG, page_size, num_pages, window, keep_first, scale, softcap, lambda, post_scale, eps, head_norm,
+                nullptr, 1};
+    return n_maps == 2 ? mma_launch<2, false>(p, n_entries, max_q, stream) : mma_launch<1, false>(p, n_entries, max_q, stream);
+}
+
+// The same for entries of one token: the heads of a KV group are the rows of a tile (nH / nG <= 16), every row's keys are
+// cut into n_splits runs, and each run's state goes to partial (float32 [N, nH, n_splits, n_maps, DV + 2]: maximum, sum,
+// weighted values), from where the kernel that merges runs (mapped_attention.cu) finishes the heads.  Entries of another
+// length are left alone.
+NG_EXPORT int ng_mapped_attention_group(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                        int table_stride, const int* cu_q, const int* ctx_before, float* partial,
+                                        int n_entries, int n_splits, int nH, int nG, int n_maps, int d, int dv, int page_size,
+                                        int num_pages, int window, int keep_first, float scale, float softcap,
+                                        cudaStream_t stream) {
+    if (n_entries <= 0) return NG_OK;
+    if (d != D || dv != DV || nH <= 0 || nG <= 0 || nH % nG || nH / nG > 16 || page_size <= 0 || n_maps < 1 || n_maps > 2 ||
+        window < 0 || keep_first < 0 || n_splits < 1 || n_splits > 65535 || !partial || ((uintptr_t)q & 15) ||
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        return NG_BAD_SIZE;
+    MmaParams p{(const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before, nullptr, 0,
+                nH, nG, page_size, num_pages, window, keep_first, scale, softcap, 0.f, 1.f, 0.f, 0, partial, n_splits};
+    return n_maps == 2 ? mma_launch<2, true>(p, n_entries, 1, stream) : mma_launch<1, true>(p, n_entries, 1, stream);
 }

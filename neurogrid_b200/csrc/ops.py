@@ -483,6 +483,42 @@ def mapped_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
              float(post_scale), float(eps), int(bool(head_norm)), _stream()), "mapped_attention_mma")
 
 
+def mapped_attention_group_takes(dim: int, vdim: int, n_heads: int, n_kv_heads: int, dtype) -> bool:
+    """Whether single-token entries can run with the heads of a KV group as the rows of a tensor-core tile."""
+    return mapped_attention_mma_takes(dim, vdim, dtype) and n_heads // n_kv_heads <= 16
+
+
+def mapped_attention_group(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                           cu_q: torch.Tensor, ctx_before: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor,
+                           partial: torch.Tensor, n_entries: int, n_heads: int, n_maps: int, window: Optional[int],
+                           keep_first: int, scale: float, softcap: float, lam: float, head_norm: bool, post_scale: float,
+                           eps: float, n_splits: int) -> None:
+    """``mapped_attention`` for a step whose entries bring one token each (bfloat16), on the tensor cores: the query
+    heads of a KV group are the rows of a tile, every row's keys are cut into ``n_splits`` runs (a block each), and the
+    runs' states pass through ``partial`` (float32, ``mapped_attention_partial_floats`` values, also for one run) to
+    the kernel that merges them, combines the maps and norms the heads."""
+    n = q.shape[0]
+    num_pages, n_k, page_size, dim = k_pages.shape
+    n_g, vdim = v_pages.shape[1], v_pages.shape[3]
+    if n_k != n_g * n_maps or q.shape != (n, n_heads * n_maps * dim) or out.shape != (n, n_heads * vdim) \
+            or q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or v_pages.dtype != torch.bfloat16 \
+            or out.dtype != torch.bfloat16 or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+        raise KernelError("mapped_attention_group: shapes or dtypes do not fit")
+    need = n * n_heads * n_splits * n_maps * (vdim + 2)
+    if partial is None or partial.dtype != torch.float32 or partial.numel() < need:
+        raise KernelError(f"mapped_attention_group: the runs need {need} float32 values")
+    _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(row_entry, "row_entry")
+    defines = {"NG_MA_D": dim, "NG_MA_DV": vdim}
+    f = _fn("mapped_attention_mma", "ng_mapped_attention_group", [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 11
+            + [_c_float] * 2 + [_c_void_p], defines)
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before), _ptr(partial),
+             n_entries, int(n_splits), n_heads, n_g, n_maps, dim, vdim, page_size, num_pages, int(window or 0), int(keep_first),
+             float(scale), float(softcap or 0.0), _stream()), "mapped_attention_group")
+    g = _fn("mapped_attention", "ng_mapped_attention_merge", [_c_void_p] * 3 + [_c_int] * 6 + [_c_float] * 3 + [_c_int, _c_int, _c_void_p])
+    _check(g(_ptr(partial), _ptr(row_entry), out.data_ptr(), _column_block(out, "attention out"), n, n_heads, n_maps, vdim,
+             int(n_splits), float(lam), float(post_scale), float(eps), int(bool(head_norm)), 1, _stream()), "mapped_attention_merge")
+
+
 # ----------------------------------------------------------------------------- input convolution
 def input_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
                ctx_before: torch.Tensor, slots: torch.Tensor, n_entries: int, max_q: int) -> None:

@@ -24,10 +24,13 @@ class MappedAttention:
     ``owns_cache`` False builds a layer that reads another layer's keys and values: it has no k/v tensors.
     Steps of few rows (and the float32 path) run a kernel with a block per row and head and cut every row's keys
     into runs so that the GPU is filled; longer bfloat16 steps run the tensor-core kernel (the float32 weights as
-    three bfloat16 terms) when the head sizes are multiples of 16 up to 128.
+    three bfloat16 terms) when the head sizes are multiples of 16 up to 128, and so do bfloat16 steps of single
+    tokens, with the heads of a KV group as the rows of a tile and every row's keys cut into runs.
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    GROUP_MAX_ROWS = 256   # decode-only steps of up to this many rows run the heads of a KV group as a tensor-core tile
+    GROUP_MAX_RUNS = 512   # ... with rows * runs a row bounded by this
     SPLIT_MAX_ROWS = 32    # steps of up to this many rows may cut each row's keys into runs
     SPLIT_MIN_KEYS = 128   # ... of at least this many keys (one tile of the kernel)
     MAX_SPLITS = 16
@@ -94,6 +97,17 @@ class MappedAttention:
         s = self.spec
         return 4 * ops.mapped_attention_partial_floats(1, s.n_heads, s.n_maps, s.value_dim, self.MAX_SPLITS)
 
+    def _longest(self, cache):
+        s = self.spec
+        longest = cache.table.shape[1] * cache.k_pages.shape[2]
+        return min(longest, s.window + s.keep_first) if s.window else longest
+
+    def _group_splits(self, n_rows, cache):
+        """Runs a row's keys are cut into when single tokens run as tiles of a KV group's heads (tiles of 64 keys)."""
+        s = self.spec
+        want = -(-3 * ops.sm_count(self.device) // max(1, n_rows * s.n_kv_heads))
+        return max(1, min(self.MAX_SPLITS, want, self._longest(cache) // 64, self.GROUP_MAX_RUNS // n_rows))
+
     # a block arrangement that ends mixer and feed-forward with ONE product calls ``core`` and multiplies itself
     def inner_width(self):
         return self.spec.n_heads * self.spec.value_dim
@@ -114,7 +128,7 @@ class MappedAttention:
         if s.window:
             longest = min(longest, s.window + s.keep_first)
         most = min(self.MAX_SPLITS, longest // self.SPLIT_MIN_KEYS)
-        if most <= 1:
+        if most <= 1 or torch.device(self.device).type != "cuda":       # (the host-side tests step the parts without a GPU)
             return 1
         return max(1, min(most, -(-6 * ops.sm_count(self.device) // max(1, n_rows * s.n_heads))))
 
@@ -146,6 +160,16 @@ class MappedAttention:
         """The attention core over the pages: q [N, n_heads * n_maps * key_dim] as the preparation left it."""
         s = self.spec
         n = q.shape[0]
+        if ctx.max_q == 1 and n <= self.GROUP_MAX_ROWS and not ctx.fixed_launches and \
+                ops.mapped_attention_group_takes(s.key_dim, s.value_dim, s.n_heads, s.n_kv_heads, self.dtype):
+            n_splits = self._group_splits(n, cache)
+            per_run = ops.mapped_attention_partial_floats(1, s.n_heads, s.n_maps, s.value_dim, 2) // 2
+            partial = ctx.ws.flat("mattn_group_partial", n * n_splits * per_run, torch.float32,
+                                  reserve=max(self.GROUP_MAX_RUNS, min(ctx.ws.max_rows, self.GROUP_MAX_ROWS)) * per_run)
+            ops.mapped_attention_group(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, ctx.row_entry,
+                                       out, partial, ctx.n_entries, s.n_heads, s.n_maps, s.window, s.keep_first,
+                                       s.softmax_scale, s.softcap or 0.0, self.lam, s.n_maps == 2, 1.0 - s.diff, s.eps, n_splits)
+            return
         if n > self.SPLIT_MAX_ROWS and ops.mapped_attention_mma_takes(s.key_dim, s.value_dim, self.dtype):
             ops.mapped_attention_mma(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
                                      ctx.n_entries, ctx.max_q, s.n_heads, s.n_maps, s.window, s.keep_first,

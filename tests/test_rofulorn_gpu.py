@@ -255,6 +255,45 @@ def test_tensor_core_kernel_with_several_entries_in_a_step():
     assert rel_err(b, a) < 1.5e-2
 
 
+@pytest.mark.parametrize("M,H,G,dim,vdim,window,keep,softcap,n_splits", [
+    (1, 8, 2, 64, 64, 200, 0, None, 3), (2, 4, 1, 32, 48, 90, 5, 7.0, 1), (2, 6, 3, 16, 128, None, 0, None, 4),
+    (1, 16, 1, 48, 16, 64, 70, 2.0, 16), (2, 3, 3, 64, 32, 33, 2, None, 2)])
+def test_single_tokens_as_tiles_of_a_group(M, H, G, dim, vdim, window, keep, softcap, n_splits):
+    """Entries of one token after contexts of every kind (nothing, less than a tile, across the kept tokens, long), a
+    padding entry between them; runs that are empty; against the row-by-row kernel."""
+    dtype, ps = torch.bfloat16, 8
+    o = ops()
+    befores = [0, 5, 63, 64, 300, 131]
+    total = [b + 1 for b in befores]
+    n_pages = sum(-(-t // ps) for t in total)
+    kp = torch.randn(n_pages, G * M, ps, dim, device=DEV).to(dtype)
+    vp = torch.randn(n_pages, G, ps, vdim, device=DEV).to(dtype)
+    table = torch.full((8, 40), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    at = 0
+    rows = [0, 1, 2, 4, 5, 6]                                  # entry 3 and 7 are padding: no rows
+    for e, t in zip(rows, total):
+        k = -(-t // ps)
+        table[e, :k] = perm[at:at + k]
+        at += k
+    table = table.to(DEV)
+    n = 8
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    cu = i32([0, 1, 2, 3, 3, 4, 5, 6, 6])
+    cb = i32([befores[0], befores[1], befores[2], 0, befores[3], befores[4], befores[5], 0])
+    pos = i32(befores + [0, 0])
+    re = i32(rows + [-1, -1])
+    q = (2 * torch.randn(n, H * M * dim, device=DEV)).to(dtype)
+    a = torch.full((n, H * vdim), 3.0, dtype=dtype, device=DEV)
+    b = torch.full((n, H * vdim), 5.0, dtype=dtype, device=DEV)
+    o.mapped_attention(q, kp, vp, table, pos, re, a, H, M, window, keep, 0.3, softcap or 0.0, 0.4, M == 2, 0.6, 1e-5)
+    partial = torch.full((n * H * n_splits * M * (vdim + 2),), float("nan"), device=DEV)
+    o.mapped_attention_group(q, kp, vp, table, cu, cb, re, b, partial, 8, H, M, window, keep, 0.3, softcap or 0.0, 0.4, M == 2,
+                             0.6, 1e-5, n_splits)
+    assert bool((b[6:] == 0).all()) and not bool(torch.isnan(b.float()).any())
+    assert rel_err(b[:6], a[:6]) < 1.5e-2
+
+
 def _mixer(spec, dtype, seed=0, owns_cache=True):
     part = build("mixer", spec, dtype=dtype, device=DEV, **({} if owns_cache else {"owns_cache": False}))
     g = torch.Generator().manual_seed(seed)
